@@ -1,0 +1,288 @@
+// Memory-bound row kernels: embedding gather, RMS norm, SiLU*mul, and the fused
+// q/k-norm + rotation + cache write that follows the QKV projection.
+//
+// Formulas (reference, Rust, f32 throughout):
+//   embedding   crates/bfi-core/src/cpu.rs:402-438
+//   RMS norm    crates/bfi-core/src/cpu.rs:92-122   y = x * rsqrt(mean(x^2) + eps) * w
+//   SiLU*mul    crates/bfi-core/src/cpu.rs:169-180, 708-720
+//   rotation    crates/bfi-core/src/cpu.rs:650-670  (NEOX: i pairs with i + n_rot/2)
+//   per-head q/k norm before the rotation, then the cache append:
+//               crates/bfi-models/src/qwen3.rs:228-234
+#include "common.cuh"
+
+// ------------------------------------------------------------------------------------------
+// embedding: out[t, :] = table[ids[t], :]   (out is the float32 residual stream)
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                  float* __restrict__ out, int width, int vocab, int* status) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* o = out + (size_t)t * width;
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0 && status) atomicOr(status, BFI_STATUS_BAD_TOKEN);
+        for (int j = threadIdx.x; j < width; j += blockDim.x) o[j] = 0.0f;
+        return;
+    }
+    const T* row = table + (size_t)id * width;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) o[j] = to_f32(row[j]);
+}
+
+extern "C" int bfi_embed_rows(const void* table, int table_dtype, const int* ids, float* out,
+                              int n_tokens, int width, int vocab, int* status, cudaStream_t stream) {
+    BFI_REQUIRE(dtype_ok(table_dtype), "embed_rows: unknown table dtype code %d", table_dtype);
+    BFI_REQUIRE(n_tokens >= 0 && width > 0 && vocab > 0, "embed_rows: bad sizes tokens=%d width=%d vocab=%d",
+                n_tokens, width, vocab);
+    if (n_tokens == 0) return 0;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (table_dtype == BFI_F32)
+        embed_rows_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, out, width, vocab, status);
+    else
+        embed_rows_kernel<bf16><<<n_tokens, threads, 0, stream>>>((const bf16*)table, ids, out, width, vocab, status);
+    return bfi_check_launch("embed_rows");
+}
+
+// ------------------------------------------------------------------------------------------
+// RMS norm over rows of the float32 residual stream (optionally a gathered subset of rows).
+// One block per output row; the sum of squares and the scale are float32.
+// ------------------------------------------------------------------------------------------
+template <typename TX>
+__global__ void rmsnorm_kernel(const TX* __restrict__ x, long x_stride, const int* __restrict__ rows,
+                               const void* __restrict__ w, int w_dtype, void* __restrict__ out,
+                               int out_dtype, long out_stride, int width, float eps) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const long src = rows ? (long)rows[r] : (long)r;
+    const TX* xr = x + src * x_stride;
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        const float v = to_f32(xr[j]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    const size_t obase = (size_t)r * out_stride;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        const float v = to_f32(xr[j]) * scale * load_as_f32(w, w_dtype, j);
+        store_from_f32(out, out_dtype, obase + j, v);
+    }
+}
+
+extern "C" int bfi_rmsnorm(const void* x, int x_dtype, long x_stride, const int* rows, const void* w,
+                           int w_dtype, void* out, int out_dtype, long out_stride, int n_rows, int width,
+                           float eps, cudaStream_t stream) {
+    BFI_REQUIRE(dtype_ok(x_dtype) && dtype_ok(w_dtype) && dtype_ok(out_dtype), "rmsnorm: unknown dtype code");
+    BFI_REQUIRE(n_rows >= 0 && width > 0, "rmsnorm: bad sizes rows=%d width=%d", n_rows, width);
+    BFI_REQUIRE(x_stride >= width && out_stride >= width, "rmsnorm: row stride shorter than the row");
+    if (n_rows == 0) return 0;
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    if (x_dtype == BFI_F32)
+        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>((const float*)x, x_stride, rows, w, w_dtype, out,
+                                                              out_dtype, out_stride, width, eps);
+    else
+        rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>((const bf16*)x, x_stride, rows, w, w_dtype, out,
+                                                             out_dtype, out_stride, width, eps);
+    return bfi_check_launch("rmsnorm");
+}
+
+// ------------------------------------------------------------------------------------------
+// SiLU(gate) * up.  `interleaved` != 0: the input row holds gate_j, up_j at columns 2j, 2j+1;
+// otherwise gate fills the first half of the row and up the second.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float silu_f32(float g) {
+    // overflow-safe two-branch sigmoid, as the reference evaluates it
+    float s;
+    if (g >= 0.0f) {
+        s = 1.0f / (1.0f + expf(-g));
+    } else {
+        const float z = expf(g);
+        s = z / (1.0f + z);
+    }
+    return g * s;
+}
+
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, long in_stride, T* __restrict__ out, long out_stride,
+                                int n_rows, int inter, int interleaved) {
+    const long total = (long)n_rows * inter;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long r = i / inter;
+        const int j = (int)(i - r * inter);
+        const T* row = gu + r * in_stride;
+        const float g = to_f32(interleaved ? row[2 * j] : row[j]);
+        const float u = to_f32(interleaved ? row[2 * j + 1] : row[inter + j]);
+        out[r * out_stride + j] = from_f32<T>(silu_f32(g) * u);
+    }
+}
+
+extern "C" int bfi_silu_mul(const void* gu, long in_stride, void* out, long out_stride, int dtype, int n_rows,
+                            int inter, int interleaved, cudaStream_t stream) {
+    BFI_REQUIRE(dtype_ok(dtype), "silu_mul: unknown dtype code %d", dtype);
+    BFI_REQUIRE(n_rows >= 0 && inter > 0, "silu_mul: bad sizes rows=%d width=%d", n_rows, inter);
+    BFI_REQUIRE(in_stride >= 2L * inter && out_stride >= inter, "silu_mul: row stride shorter than the row");
+    if (n_rows == 0) return 0;
+    const long total = (long)n_rows * inter;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148L * 16 ? (total + threads - 1) / threads : 148L * 16);
+    if (dtype == BFI_F32)
+        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, in_stride, (float*)out, out_stride,
+                                                               n_rows, inter, interleaved);
+    else
+        silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, in_stride, (bf16*)out, out_stride,
+                                                              n_rows, inter, interleaved);
+    return bfi_check_launch("silu_mul");
+}
+
+// ------------------------------------------------------------------------------------------
+// After the QKV projection: per token and head, RMS norm over head_dim (q and k), rotate-half
+// rotation by the token's position (q and k), then q back in place and k, v into the cache page
+// of the token's slot.  One warp per (token, head); the head passes through shared memory so
+// any head_dim that is a multiple of 16 (up to 512) works.
+//
+//   qkv          [tokens, (n_q + n_kv_in*2) * d]   n_kv_in = 0 when the run reads another run's cache
+//   rope_table   [positions, rot_dim/2] of (cos, sin), float32, or null for no rotation
+//   flags        bit 0: write k, v into the cache;  bit 1: write k back in place as well
+// ------------------------------------------------------------------------------------------
+#define QKR_WARPS 4
+#define QKR_MAX_D 512
+
+template <typename T>
+__global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, long token_stride, int n_tokens, int n_q, int n_kv,
+                                          int d, const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w,
+                                          int norm_dtype, float eps, const float2* __restrict__ rope_table,
+                                          int rot_dim, int table_positions, const int* __restrict__ token_pos,
+                                          const int* __restrict__ token_slot, T* __restrict__ k_pages,
+                                          T* __restrict__ v_pages, const int* __restrict__ block_table,
+                                          int table_stride, int flags, int* status) {
+    __shared__ float buf[QKR_WARPS][QKR_MAX_D];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads = n_q + 2 * n_kv;
+    const long item = (long)blockIdx.x * QKR_WARPS + warp;
+    if (item >= (long)n_tokens * heads) return;
+    const int t = (int)(item / heads);
+    const int hh = (int)(item - (long)t * heads);
+    const int slot = token_slot[t];
+    if (slot < 0) return;  // padding row
+    const int pos = token_pos[t];
+    const int kind = hh < n_q ? 0 : (hh < n_q + n_kv ? 1 : 2);  // q, k, v
+    T* src = qkv + (size_t)t * token_stride + (size_t)hh * d;
+    float* b = buf[warp];
+
+    float ss = 0.0f;
+    for (int j = lane; j < d; j += 32) {
+        const float v = to_f32(src[j]);
+        b[j] = v;
+        ss = fmaf(v, v, ss);
+    }
+    const void* nw = kind == 0 ? q_norm_w : (kind == 1 ? k_norm_w : nullptr);
+    if (nw != nullptr) {
+        ss = warp_sum(ss);
+        const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+        for (int j = lane; j < d; j += 32) b[j] = b[j] * scale * load_as_f32(nw, norm_dtype, j);
+    }
+    __syncwarp();
+
+    // destination
+    T* dst_cache = nullptr;
+    if (kind != 0 && (flags & 1)) {
+        const int page = block_table[(size_t)slot * table_stride + pos / BFI_PAGE_TOKENS];
+        if (page < 0) {
+            if (lane == 0 && status) atomicOr(status, BFI_STATUS_NO_PAGE);
+        } else {
+            T* pages = kind == 1 ? k_pages : v_pages;
+            const int h = kind == 1 ? hh - n_q : hh - n_q - n_kv;
+            dst_cache = pages + (((size_t)page * n_kv + h) * BFI_PAGE_TOKENS + (pos % BFI_PAGE_TOKENS)) * d;
+        }
+    }
+    const bool in_place = kind == 0 || (kind == 1 && (flags & 2));
+
+    if (kind != 2 && rope_table != nullptr) {
+        if (pos < 0 || pos >= table_positions) {
+            if (lane == 0 && status) atomicOr(status, BFI_STATUS_BAD_POSITION);
+            return;
+        }
+        const int half = rot_dim >> 1;
+        const float2* cs = rope_table + (size_t)pos * half;
+        for (int i = lane; i < half; i += 32) {
+            const float2 c = cs[i];
+            const float x0 = b[i], x1 = b[i + half];
+            const float o0 = x0 * c.x - x1 * c.y;
+            const float o1 = x0 * c.y + x1 * c.x;
+            if (in_place) {
+                src[i] = from_f32<T>(o0);
+                src[i + half] = from_f32<T>(o1);
+            }
+            if (dst_cache) {
+                dst_cache[i] = from_f32<T>(o0);
+                dst_cache[i + half] = from_f32<T>(o1);
+            }
+        }
+        for (int j = rot_dim + lane; j < d; j += 32) {
+            if (in_place) src[j] = from_f32<T>(b[j]);
+            if (dst_cache) dst_cache[j] = from_f32<T>(b[j]);
+        }
+    } else {
+        for (int j = lane; j < d; j += 32) {
+            if (in_place && nw != nullptr) src[j] = from_f32<T>(b[j]);
+            if (dst_cache) dst_cache[j] = from_f32<T>(b[j]);
+        }
+    }
+}
+
+extern "C" int bfi_qk_norm_rope_cache(void* qkv, int dtype, long token_stride, int n_tokens, int n_q, int n_kv,
+                                      int d, const void* q_norm_w, const void* k_norm_w, int norm_dtype, float eps,
+                                      const void* rope_table, int rot_dim, int table_positions,
+                                      const int* token_pos, const int* token_slot, void* k_pages, void* v_pages,
+                                      const int* block_table, int table_stride, int flags, int* status,
+                                      cudaStream_t stream) {
+    BFI_REQUIRE(dtype_ok(dtype) && dtype_ok(norm_dtype), "qk_norm_rope_cache: unknown dtype code");
+    BFI_REQUIRE(n_tokens >= 0 && n_q >= 0 && n_kv >= 0 && n_q + n_kv > 0, "qk_norm_rope_cache: bad head counts q=%d kv=%d",
+                n_q, n_kv);
+    BFI_REQUIRE(d > 0 && d % 2 == 0 && d <= QKR_MAX_D, "qk_norm_rope_cache: head_dim %d must be even and at most %d",
+                d, QKR_MAX_D);
+    BFI_REQUIRE(token_stride >= (long)(n_q + 2 * n_kv) * d, "qk_norm_rope_cache: token stride shorter than the heads");
+    if (rope_table) {
+        BFI_REQUIRE(rot_dim > 0 && rot_dim % 2 == 0 && rot_dim <= d,
+                    "qk_norm_rope_cache: rotary width %d must be even and at most head_dim %d", rot_dim, d);
+        BFI_REQUIRE(table_positions > 0, "qk_norm_rope_cache: empty rotation table");
+    }
+    if ((flags & 1) && n_kv > 0)
+        BFI_REQUIRE(k_pages && v_pages && block_table && table_stride > 0, "qk_norm_rope_cache: cache write without a cache");
+    if (n_tokens == 0) return 0;
+    const long items = (long)n_tokens * (n_q + 2 * n_kv);
+    const int blocks = (int)((items + QKR_WARPS - 1) / QKR_WARPS);
+    if (dtype == BFI_F32)
+        qk_norm_rope_cache_kernel<float><<<blocks, QKR_WARPS * 32, 0, stream>>>(
+            (float*)qkv, token_stride, n_tokens, n_q, n_kv, d, q_norm_w, k_norm_w, norm_dtype, eps,
+            (const float2*)rope_table, rot_dim, table_positions, token_pos, token_slot, (float*)k_pages,
+            (float*)v_pages, block_table, table_stride, flags, status);
+    else
+        qk_norm_rope_cache_kernel<bf16><<<blocks, QKR_WARPS * 32, 0, stream>>>(
+            (bf16*)qkv, token_stride, n_tokens, n_q, n_kv, d, q_norm_w, k_norm_w, norm_dtype, eps,
+            (const float2*)rope_table, rot_dim, table_positions, token_pos, token_slot, (bf16*)k_pages,
+            (bf16*)v_pages, block_table, table_stride, flags, status);
+    return bfi_check_launch("qk_norm_rope_cache");
+}
+
+// ------------------------------------------------------------------------------------------
+// Small utilities
+// ------------------------------------------------------------------------------------------
+// out[i] += add[i]  (float32 residual stream += an activation)
+template <typename T>
+__global__ void residual_add_kernel(float* __restrict__ x, const T* __restrict__ y, long n) {
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x)
+        x[i] += to_f32(y[i]);
+}
+
+extern "C" int bfi_residual_add(float* x, const void* y, int y_dtype, long n, cudaStream_t stream) {
+    BFI_REQUIRE(dtype_ok(y_dtype), "residual_add: unknown dtype code %d", y_dtype);
+    if (n <= 0) return 0;
+    const int threads = 256;
+    const long want = (n + threads - 1) / threads;
+    const int blocks = (int)(want < 148L * 16 ? want : 148L * 16);
+    if (y_dtype == BFI_F32)
+        residual_add_kernel<float><<<blocks, threads, 0, stream>>>(x, (const float*)y, n);
+    else
+        residual_add_kernel<bf16><<<blocks, threads, 0, stream>>>(x, (const bf16*)y, n);
+    return bfi_check_launch("residual_add");
+}

@@ -1,0 +1,233 @@
+// Choosing the next token from float32 logits on the device: greedy, and temperature sampling
+// with the reference's penalties and min-p cut, one block per row.
+//
+// Reference (crates/bfi-runtime/src/sample.rs):
+//   argmax            :429-439  strict '>' scan from index 0, so the lowest index among equal maxima wins
+//   repeat penalty    :345-357  every id seen so far: logit > 0 ? logit / pen : logit * pen
+//   presence penalty  :359-367  logit -= pen for every seen id, after the repeat penalty
+//   temperature       :369-390  <= 0 means argmax; else logits / T, max-subtracted softmax
+//   min-p             :411-424  keep p >= min_p * p_max
+//   draw              :312-323  r = u * sum(kept); the first kept id, in vocabulary order, whose running sum reaches r
+// Top-k and top-p need a sort and are handled outside this file.
+#include "common.cuh"
+
+#define SAMPLE_THREADS 1024
+#define SAMPLE_ITEMS 4
+
+struct ArgBest {
+    float v;
+    int i;
+};
+
+__device__ __forceinline__ ArgBest better(ArgBest a, ArgBest b) {
+    if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+    return a;
+}
+
+__device__ __forceinline__ ArgBest block_argmax(ArgBest mine, ArgBest* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n_warps = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgBest other;
+        other.v = __shfl_xor_sync(0xffffffffu, mine.v, o);
+        other.i = __shfl_xor_sync(0xffffffffu, mine.i, o);
+        mine = better(mine, other);
+    }
+    __syncthreads();
+    if (lane == 0) scratch[warp] = mine;
+    __syncthreads();
+    if (warp == 0) {
+        ArgBest t;
+        t.v = -INFINITY;
+        t.i = 0x7fffffff;
+        if (lane < n_warps) t = scratch[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            ArgBest other;
+            other.v = __shfl_xor_sync(0xffffffffu, t.v, o);
+            other.i = __shfl_xor_sync(0xffffffffu, t.i, o);
+            t = better(t, other);
+        }
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+// Applies the penalties for one seen id list to a row held in global memory (work row).
+__device__ __forceinline__ float penalised(float v, float repeat_penalty, float presence_penalty) {
+    if (repeat_penalty != 1.0f) v = v > 0.0f ? v / repeat_penalty : v * repeat_penalty;
+    return v - presence_penalty;
+}
+
+// One block per row.
+//   logits        [rows, stride] float32 (never modified)
+//   work          [rows, vocab] float32 scratch, needed only when a row has seen ids (else may be null)
+//   seen, seen_cu ids seen by each row, every id at most once per row; seen_cu [rows+1] offsets (null: none)
+//   temperature, u per row.  u in [0, 1).
+//   out           [rows] int32
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_rows_kernel(const float* __restrict__ logits, long stride, float* __restrict__ work, int vocab,
+                   const int* __restrict__ seen, const int* __restrict__ seen_cu, const float* __restrict__ temperature,
+                   const float* __restrict__ u_draw, float repeat_penalty, float presence_penalty, float min_p,
+                   int* __restrict__ out) {
+    __shared__ ArgBest abest[33];
+    __shared__ float fscratch[33];
+    __shared__ float warp_tot[32];
+    __shared__ int found;
+    const int row = blockIdx.x;
+    const float* x = logits + (size_t)row * stride;
+
+    // ---- penalties: copy the row and edit the seen ids
+    const int n_seen = seen_cu ? seen_cu[row + 1] - seen_cu[row] : 0;
+    if (n_seen > 0 && (repeat_penalty != 1.0f || presence_penalty != 0.0f)) {
+        float* w = work + (size_t)row * vocab;
+        for (int j = threadIdx.x; j < vocab; j += blockDim.x) w[j] = x[j];
+        __syncthreads();
+        const int* ids = seen + seen_cu[row];
+        for (int s = threadIdx.x; s < n_seen; s += blockDim.x) {
+            const int id = ids[s];
+            if (id >= 0 && id < vocab) w[id] = penalised(w[id], repeat_penalty, presence_penalty);
+        }
+        __syncthreads();
+        x = w;
+    }
+
+    // ---- maximum and its lowest index
+    ArgBest mine;
+    mine.v = -INFINITY;
+    mine.i = 0x7fffffff;
+    for (int j = threadIdx.x; j < vocab; j += blockDim.x) {
+        const float v = x[j];
+        if (v > mine.v) {  // strict: within a thread indices ascend, so the first maximum stays
+            mine.v = v;
+            mine.i = j;
+        }
+    }
+    const ArgBest best = block_argmax(mine, abest);
+    const int arg = best.i == 0x7fffffff ? 0 : best.i;
+    const float temp = temperature[row];
+    if (!(temp > 0.0f)) {
+        if (threadIdx.x == 0) out[row] = arg;
+        return;
+    }
+
+    // ---- softmax denominators.  e_j = exp((x_j - max) / T); p_j = e_j / sum; p_max = 1 / sum.
+    const float inv_t = 1.0f / temp;
+    const float mx = best.v;
+    float part = 0.0f, kept = 0.0f;
+    for (int j = threadIdx.x; j < vocab; j += blockDim.x) {
+        const float e = expf((x[j] - mx) * inv_t);
+        part += e;
+        if (e >= min_p) kept += e;   // p_j >= min_p * p_max  <=>  e_j >= min_p
+    }
+    const float total = block_sum(part, fscratch);
+    const float total_kept = min_p > 0.0f ? block_sum(kept, fscratch) : total;
+    if (!(total > 0.0f) || !(total_kept > 0.0f)) {
+        if (threadIdx.x == 0) out[row] = arg;
+        return;
+    }
+    const float r = u_draw[row] * total_kept;
+
+    // ---- inverse CDF in vocabulary order: chunks of SAMPLE_THREADS * SAMPLE_ITEMS consecutive ids
+    if (threadIdx.x == 0) found = 0x7fffffff;
+    __syncthreads();
+    float running = 0.0f;
+    int last_kept = -1;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int base = 0; base < vocab; base += SAMPLE_THREADS * SAMPLE_ITEMS) {
+        float e[SAMPLE_ITEMS];
+        float local = 0.0f;
+        const int j0 = base + threadIdx.x * SAMPLE_ITEMS;
+#pragma unroll
+        for (int k = 0; k < SAMPLE_ITEMS; ++k) {
+            const int j = j0 + k;
+            float v = 0.0f;
+            if (j < vocab) {
+                v = expf((x[j] - mx) * inv_t);
+                if (v < min_p) v = 0.0f;
+            }
+            e[k] = v;
+            local += v;
+        }
+        // exclusive prefix of `local` over the block
+        float incl = local;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        if (lane == 31) warp_tot[warp] = incl;
+        __syncthreads();
+        float before = running;
+        for (int w2 = 0; w2 < warp; ++w2) before += warp_tot[w2];
+        float chunk_total = 0.0f;
+        for (int w2 = 0; w2 < (SAMPLE_THREADS >> 5); ++w2) chunk_total += warp_tot[w2];
+        float cum = before + (incl - local);
+#pragma unroll
+        for (int k = 0; k < SAMPLE_ITEMS; ++k) {
+            if (e[k] > 0.0f) {
+                cum += e[k];
+                last_kept = j0 + k;
+                if (r <= cum) {
+                    atomicMin(&found, j0 + k);
+                    break;
+                }
+            }
+        }
+        running += chunk_total;
+        __syncthreads();
+        if (found != 0x7fffffff) break;
+    }
+    if (found == 0x7fffffff) {
+        // rounding left r above the final running sum: the last kept id, as the reference does
+        const float m = block_max((float)last_kept, fscratch);
+        if (threadIdx.x == 0) out[row] = m >= 0.0f ? (int)m : arg;
+        return;
+    }
+    if (threadIdx.x == 0) out[row] = found;
+}
+
+extern "C" int bfi_sample_rows(const float* logits, long stride, float* work, int n_rows, int vocab, const int* seen,
+                               const int* seen_cu, const float* temperature, const float* u_draw, float repeat_penalty,
+                               float presence_penalty, float min_p, int* out, cudaStream_t stream) {
+    BFI_REQUIRE(n_rows >= 0 && vocab > 0, "sample_rows: bad sizes rows=%d vocab=%d", n_rows, vocab);
+    BFI_REQUIRE(stride >= vocab, "sample_rows: row stride shorter than the vocabulary");
+    BFI_REQUIRE(temperature && u_draw && out && logits, "sample_rows: null argument");
+    BFI_REQUIRE(vocab < (1 << 24), "sample_rows: vocabulary %d too large", vocab);
+    if (seen_cu && (repeat_penalty != 1.0f || presence_penalty != 0.0f))
+        BFI_REQUIRE(work != nullptr && seen != nullptr, "sample_rows: penalties need a work buffer and the seen ids");
+    BFI_REQUIRE(repeat_penalty > 0.0f, "sample_rows: repeat_penalty must be positive");
+    if (n_rows == 0) return 0;
+    sample_rows_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, stride, work, vocab, seen, seen_cu, temperature,
+                                                             u_draw, repeat_penalty, presence_penalty, min_p, out);
+    return bfi_check_launch("sample_rows");
+}
+
+// Greedy only: out[row] = lowest index of the row maximum.
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+argmax_rows_kernel(const float* __restrict__ logits, long stride, int vocab, int* __restrict__ out) {
+    __shared__ ArgBest abest[33];
+    const float* x = logits + (size_t)blockIdx.x * stride;
+    ArgBest mine;
+    mine.v = -INFINITY;
+    mine.i = 0x7fffffff;
+    for (int j = threadIdx.x; j < vocab; j += blockDim.x) {
+        const float v = x[j];
+        if (v > mine.v) {
+            mine.v = v;
+            mine.i = j;
+        }
+    }
+    const ArgBest best = block_argmax(mine, abest);
+    if (threadIdx.x == 0) out[blockIdx.x] = best.i == 0x7fffffff ? 0 : best.i;
+}
+
+extern "C" int bfi_argmax_rows(const float* logits, long stride, int n_rows, int vocab, int* out, cudaStream_t stream) {
+    BFI_REQUIRE(n_rows >= 0 && vocab > 0, "argmax_rows: bad sizes rows=%d vocab=%d", n_rows, vocab);
+    BFI_REQUIRE(stride >= vocab, "argmax_rows: row stride shorter than the vocabulary");
+    if (n_rows == 0) return 0;
+    argmax_rows_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, stride, vocab, out);
+    return bfi_check_launch("argmax_rows");
+}

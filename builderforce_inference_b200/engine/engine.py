@@ -1,0 +1,360 @@
+"""The engine: a decoder, its cache, and ONE step function.
+
+``Engine.step`` takes a batch of sequences, each with the next tokens it brings (a whole prompt,
+a further piece of one, or a single token), runs exactly those tokens as one packed batch from
+the cache that earlier steps left, and returns float32 logits at the wanted places.  It is what
+generation, trace replay, the benchmark and the tests all drive; there is no second forward pass.
+
+The reference's counterpart is ``Model::forward`` / ``forward_each`` for one sequence
+(crates/bfi-models/src/arch.rs:29-59; qwen3.rs:190-314) looped over by the runtime
+(crates/bfi-runtime/src/engine/mod.rs:297-337); here the batch reaches the kernels.
+
+Steps in which every sequence brings one token are captured in CUDA graphs, one per padded batch
+size, when every part of the model is graph-safe.  Padding rows carry slot -1, which every kernel
+skips, so padding changes no result.
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache.cache import SequenceCache
+from ..cache.pages import PAGE_TOKENS, CacheError
+from ..config.base import ConfigError, read_json
+from ..kernels import ops
+from ..parts.base import ModelSpec
+from ..registry import describe_model
+from ..weights.loader import load_folder
+from ..weights.random_init import random_tensors
+from .context import StepContext, Workspace
+from .decoder import Decoder, Runtime, expected_tensors
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+class StepError(RuntimeError):
+    """A step was refused before any launch, or a device-side check recorded a fault."""
+
+
+@dataclass
+class SequenceStep:
+    """What one sequence brings to a step: its next tokens, and the places among them whose
+    logits are wanted (indices into ``tokens``; may be empty)."""
+
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+def parse_dtype(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        if name not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"run dtype must be bfloat16 or float32, got {name}")
+        return name
+    if name not in DTYPES:
+        raise ValueError(f"run dtype must be one of {sorted(DTYPES)}, got {name!r}")
+    return DTYPES[name]
+
+
+def _require_gpu(device: torch.device) -> None:
+    if device.type != "cuda" or not torch.cuda.is_available():
+        raise RuntimeError("this engine runs on an NVIDIA GPU only (sm_100a kernels); no CUDA device is available")
+
+
+class _DecodeGraph:
+    """A captured single-token step for one padded batch size."""
+
+    def __init__(self, engine: "Engine", batch: int):
+        self.batch = batch
+        dev = engine.device
+        self.meta = torch.zeros(engine._meta_len(batch, batch, 0), dtype=torch.int32, device=dev)
+        self.logits = torch.empty((batch, engine.spec.vocab_size), dtype=torch.float32, device=dev)
+        self.rows = torch.arange(batch, dtype=torch.int32, device=dev)
+        self.stamp = engine._stamp()
+        # every row starts as padding (slot -1), so the runs below touch no sequence's cache
+        engine._fill_meta(self.meta, [], [], [], [0], batch, batch)
+        ctx = engine._context_from_meta(self.meta, batch, batch, 1, None)
+        # eager run first: loads kernels, sizes the workspace, sets launch attributes
+        engine._forward(ctx, self.rows, self.logits)
+        torch.cuda.synchronize(dev)
+        if self.stamp != engine._stamp():
+            self.stamp = engine._stamp()
+            ctx = engine._context_from_meta(self.meta, batch, batch, 1, None)
+        ctx.capturing = True
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            engine._forward(ctx, self.rows, self.logits)
+
+
+class Engine:
+    """A loaded model with its cache.  Build with ``Engine.load`` or ``Engine.from_random``."""
+
+    def __init__(self, spec: ModelSpec, tensors: Dict[str, torch.Tensor], dtype: torch.dtype,
+                 device: torch.device, max_tokens: int, max_seq_len: Optional[int] = None,
+                 use_graphs: bool = True, prefill_chunk_tokens: int = 8192,
+                 config: Optional[Dict[str, Any]] = None):
+        _require_gpu(device)
+        self.spec = spec
+        self.config = config
+        self.dtype = dtype
+        self.device = device
+        limit = spec.max_positions if spec.max_positions > 0 else max_tokens
+        self.max_seq_len = min(limit, max_seq_len) if max_seq_len else limit
+        self.max_seq_len = max(1, min(self.max_seq_len,
+                                      ((max_tokens + PAGE_TOKENS - 1) // PAGE_TOKENS) * PAGE_TOKENS))
+        self.runtime = Runtime(device, dtype)
+        self.decoder = Decoder(spec, self.runtime)
+        self.decoder.load(tensors, self.max_seq_len)
+        self.cache = SequenceCache(self.decoder.run_needs(), self.decoder.run_cache_of(), max_tokens,
+                                   self.max_seq_len, dtype, device)
+        self.workspace = Workspace(device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.prefill_chunk_tokens = max(PAGE_TOKENS, int(prefill_chunk_tokens))
+        self.use_graphs = bool(use_graphs) and self.decoder.graph_safe()
+        self._graphs: Dict[int, _DecodeGraph] = {}
+        self._pinned: Dict[int, torch.Tensor] = {}
+        self.kernel_launches = 0       # steps' kernels are counted by the benchmark through this hook
+
+    # ---- construction ----------------------------------------------------------------
+    @classmethod
+    def load(cls, folder: str, dtype="bfloat16", max_tokens: int = 16384, max_seq_len: Optional[int] = None,
+             device="cuda:0", **kw) -> "Engine":
+        """Load ``folder`` (config.json + model.safetensors); the model class comes from config.json."""
+        dt = parse_dtype(dtype)
+        dev = torch.device(device)
+        _require_gpu(dev)
+        config = read_json(os.path.join(folder, "config.json"))
+        spec = describe_model(config)
+        tensors = load_folder(folder, expected_tensors(spec), spec.ignored_names, dt, dev)
+        return cls(spec, tensors, dt, dev, max_tokens, max_seq_len, config=config, **kw)
+
+    @classmethod
+    def from_random(cls, config: Dict[str, Any], seed: int, dtype="bfloat16", max_tokens: int = 16384,
+                    max_seq_len: Optional[int] = None, device="cuda:0", **kw) -> "Engine":
+        """Random weights made directly in device memory (same distributions as a written folder)."""
+        dt = parse_dtype(dtype)
+        dev = torch.device(device)
+        _require_gpu(dev)
+        spec = describe_model(config)
+        tensors = dict(random_tensors(expected_tensors(spec), seed, dt, dev))
+        return cls(spec, tensors, dt, dev, max_tokens, max_seq_len, config=config, **kw)
+
+    # ---- slots -----------------------------------------------------------------------
+    def acquire(self) -> int:
+        return self.cache.acquire()
+
+    def release(self, slot: int) -> None:
+        self.cache.release(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # ---- the step function -----------------------------------------------------------
+    def step(self, seqs: Sequence[SequenceStep], check: bool = True) -> torch.Tensor:
+        """Run the given tokens of the given sequences as one batch; returns float32 logits
+        ``[wanted, vocab]`` on the device, in the order of ``seqs`` and of each ``want``.
+        The tensor is valid until the next call of ``step``."""
+        if not seqs:
+            raise StepError("a step needs at least one sequence")
+        vocab = self.spec.vocab_size
+        slots, counts = [], []
+        for s in seqs:
+            n = len(s.tokens)
+            if n == 0:
+                raise StepError(f"slot {s.slot}: empty token list")
+            for t in s.tokens:
+                if not 0 <= int(t) < vocab:
+                    raise StepError(f"slot {s.slot}: token id {t} out of range for vocabulary {vocab}")
+            for w in s.want:
+                if not 0 <= int(w) < n:
+                    raise StepError(f"slot {s.slot}: wanted place {w} is not among its {n} tokens")
+            slots.append(int(s.slot))
+            counts.append(n)
+        try:
+            self.cache.begin_step(slots, counts)
+        except CacheError as e:
+            raise StepError(str(e)) from e
+        starts = [self.cache.length(s) for s in slots]
+
+        if all(c == 1 for c in counts):
+            out = self._decode_step(seqs, slots, starts)
+        else:
+            out = self._prefill_step(seqs, slots, starts, counts)
+        self.cache.end_step(slots, counts)
+        if check:
+            self.check_status()
+        return out
+
+    def check_status(self) -> None:
+        bits = int(self.status.item())
+        if bits:
+            self.status.zero_()
+            what = []
+            if bits & ops.STATUS_BAD_TOKEN:
+                what.append("a token id outside the vocabulary reached the embedding")
+            if bits & ops.STATUS_NO_PAGE:
+                what.append("a token had no cache page to be written to")
+            if bits & ops.STATUS_BAD_POSITION:
+                what.append("a position outside the rotation table")
+            raise StepError("device-side check failed: " + "; ".join(what))
+
+    # ---- single-token steps ----------------------------------------------------------
+    def _decode_step(self, seqs, slots, starts) -> torch.Tensor:
+        b = len(seqs)
+        tokens = [int(s.tokens[0]) for s in seqs]
+        want_rows = [i for i, s in enumerate(seqs) if len(s.want) > 0]
+        if self.use_graphs:
+            padded = 1
+            while padded < b:
+                padded *= 2
+            if padded > 16:
+                padded = ((b + 15) // 16) * 16
+            g = self._graphs.get(padded)
+            if g is None or g.stamp != self._stamp():
+                g = _DecodeGraph(self, padded)
+                self._graphs[padded] = g
+            self._fill_meta(g.meta, tokens, starts, slots, list(range(b + 1)), padded, padded)
+            g.graph.replay()
+            logits = g.logits
+        else:
+            meta = self._meta_buffer(b, b, 0)
+            self._fill_meta(meta, tokens, starts, slots, list(range(b + 1)), b, b)
+            ctx = self._context_from_meta(meta, b, b, 1, (slots, starts, [1] * b))
+            logits = self.workspace.rows("logits", b, self.spec.vocab_size, torch.float32)
+            rows = torch.arange(b, dtype=torch.int32, device=self.device)
+            self._forward(ctx, rows, logits)
+        if len(want_rows) == b:
+            return logits[:b]
+        if not want_rows:
+            return logits[:0]
+        idx = torch.tensor(want_rows, dtype=torch.long, device=self.device)
+        return logits.index_select(0, idx)
+
+    # ---- steps with longer pieces ----------------------------------------------------
+    def _prefill_step(self, seqs, slots, starts, counts) -> torch.Tensor:
+        n_want = sum(len(s.want) for s in seqs)
+        out = self.workspace.rows("logits.prefill", max(n_want, 1), self.spec.vocab_size, torch.float32)[:n_want]
+        # cut into micro-batches of at most prefill_chunk_tokens tokens; a long sequence is cut too
+        budget = self.prefill_chunk_tokens
+        pieces: List[List[Tuple[int, int, int]]] = [[]]      # (sequence index, first token, count)
+        used = 0
+        for i, n in enumerate(counts):
+            off = 0
+            while off < n:
+                if used == budget:
+                    pieces.append([])
+                    used = 0
+                take = min(n - off, budget - used)
+                pieces[-1].append((i, off, take))
+                used += take
+                off += take
+        # where each wanted place lands in `out`
+        want_base = []
+        acc = 0
+        for s in seqs:
+            want_base.append(acc)
+            acc += len(s.want)
+        for piece in pieces:
+            tok, pos, slot_of, cu, p_slots, p_starts, p_counts = [], [], [], [0], [], [], []
+            rows, dest = [], []
+            for (i, off, take) in piece:
+                s = seqs[i]
+                base = len(tok)
+                tok.extend(int(t) for t in s.tokens[off:off + take])
+                pos.extend(range(starts[i] + off, starts[i] + off + take))
+                slot_of.extend([slots[i]] * take)
+                cu.append(len(tok))
+                p_slots.append(slots[i])
+                p_starts.append(starts[i] + off)
+                p_counts.append(take)
+                for j, w in enumerate(s.want):
+                    if off <= w < off + take:
+                        rows.append(base + (w - off))
+                        dest.append(want_base[i] + j)
+            n_tok, n_seq = len(tok), len(piece)
+            meta = self._meta_buffer(n_tok, n_seq, len(rows))
+            self._fill_meta(meta, tok, pos, slot_of, cu, n_tok, n_seq, p_slots, p_starts, rows)
+            ctx = self._context_from_meta(meta, n_tok, n_seq, max(p_counts), (p_slots, p_starts, p_counts))
+            x = self.decoder.embed(ctx)
+            self.decoder.run_layers(ctx, x, self.cache)
+            if rows:
+                row_idx = self._meta_slices(meta, n_tok, n_seq, len(rows))[6]
+                contiguous = dest == list(range(dest[0], dest[0] + len(dest)))
+                if contiguous:
+                    self.decoder.logits(ctx, x, row_idx, out[dest[0]:dest[0] + len(dest)])
+                else:
+                    tmp = self.workspace.rows("logits.tmp", len(rows), self.spec.vocab_size, torch.float32)
+                    self.decoder.logits(ctx, x, row_idx, tmp)
+                    out.index_copy_(0, torch.tensor(dest, dtype=torch.long, device=self.device), tmp)
+        return out
+
+    # ---- one forward over a prepared context -----------------------------------------
+    def _forward(self, ctx: StepContext, rows: torch.Tensor, logits: torch.Tensor) -> None:
+        x = self.decoder.embed(ctx)
+        self.decoder.run_layers(ctx, x, self.cache)
+        self.decoder.logits(ctx, x, rows, logits[:rows.numel()])
+
+    # ---- the packed index arrays of a step -------------------------------------------
+    # layout of `meta` (int32): token_ids[T] token_pos[T] token_slot[T] cu_seqlens[B+1] seq_slot[B]
+    #                           seq_start[B] want_rows[W]
+    @staticmethod
+    def _meta_len(n_tok: int, n_seq: int, n_want: int) -> int:
+        return 3 * n_tok + (n_seq + 1) + 2 * n_seq + n_want
+
+    def _meta_buffer(self, n_tok: int, n_seq: int, n_want: int) -> torch.Tensor:
+        n = self._meta_len(n_tok, n_seq, n_want)
+        return self.workspace.vector("meta", n, torch.int32)
+
+    @staticmethod
+    def _meta_slices(meta, n_tok, n_seq, n_want):
+        o = 0
+        out = []
+        for n in (n_tok, n_tok, n_tok, n_seq + 1, n_seq, n_seq, n_want):
+            out.append(meta[o:o + n])
+            o += n
+        return out
+
+    def _fill_meta(self, meta, tok, pos, slot_of, cu, n_tok, n_seq, seq_slots=None, seq_starts=None,
+                   want_rows=()) -> None:
+        """Pack the step's index arrays on the host and copy them to ``meta`` in one transfer.
+        In a single-token step ``pos`` doubles as the sequences' starts and ``slot_of`` as their slots."""
+        if seq_slots is None:
+            seq_slots, seq_starts = slot_of, pos
+        pad_t = n_tok - len(tok)
+        pad_s = n_seq - len(seq_slots)
+        last = cu[-1]
+        host = (list(tok) + [0] * pad_t + list(pos) + [0] * pad_t + list(slot_of) + [-1] * pad_t
+                + list(cu) + [last] * pad_s + list(seq_slots) + [-1] * pad_s
+                + list(seq_starts) + [0] * pad_s + list(want_rows))
+        n = len(host)
+        pinned = self._pinned.get(n)
+        if pinned is None:
+            pinned = torch.empty(n, dtype=torch.int32, pin_memory=True)
+            self._pinned[n] = pinned
+        else:
+            # the previous copy from this buffer must have been consumed before it is rewritten
+            torch.cuda.current_stream(self.device).synchronize()
+        pinned.copy_(torch.tensor(host, dtype=torch.int32))
+        meta[:n].copy_(pinned, non_blocking=True)
+
+    def _context_from_meta(self, meta, n_tok, n_seq, max_seq_tokens, host) -> StepContext:
+        ids, pos, slot_of, cu, seq_slot, seq_start, _ = self._meta_slices(meta, n_tok, n_seq, 0)
+        ctx = StepContext(
+            n_tokens=n_tok, n_seqs=n_seq, max_seq_tokens=max_seq_tokens, act_dtype=self.dtype,
+            workspace=self.workspace, token_ids=ids, token_pos=pos, token_slot=slot_of, cu_seqlens=cu,
+            seq_slot=seq_slot, seq_start=seq_start, status=self.status)
+        if host is not None:
+            ctx.host_seq_slot, ctx.host_seq_start, ctx.host_seq_tokens = host
+        return ctx
+
+    def _stamp(self) -> Tuple[int, int]:
+        return (self.workspace.generation, self.cache.generation)
+
+    # ---- accounting ------------------------------------------------------------------
+    def decode_step_bytes(self) -> int:
+        """Bytes a single-token step has to read: every weight once and the live sequences' cache."""
+        return self.decoder.n_weight_bytes + self.cache.live_kv_bytes()

@@ -1,0 +1,59 @@
+"""Loading the compiled kernel libraries and calling their exported C functions.
+
+There is no other implementation behind these calls: if a library cannot be built or loaded,
+or a function reports an error, a ``KernelError`` is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Dict
+
+from ..csrc import build as _build
+
+
+class KernelError(RuntimeError):
+    """A kernel library is missing, or one of its functions refused its arguments."""
+
+
+_lock = threading.Lock()
+_loaded: Dict[str, "KernelLibrary"] = {}
+
+
+class KernelLibrary:
+    def __init__(self, name: str):
+        try:
+            self.path = _build.library_path(name)
+        except _build.BuildError as e:
+            raise KernelError(f"kernel library '{name}' is not available: {e}") from e
+        try:
+            self.lib = ctypes.CDLL(self.path)
+        except OSError as e:
+            raise KernelError(f"kernel library '{name}' ({self.path}) cannot be loaded: {e}") from e
+        self.name = name
+        self.lib.bfi_last_error.restype = ctypes.c_char_p
+        self._funcs: Dict[str, ctypes._CFuncPtr] = {}
+
+    def call(self, func: str, *args) -> None:
+        f = self._funcs.get(func)
+        if f is None:
+            try:
+                f = getattr(self.lib, func)
+            except AttributeError as e:
+                raise KernelError(f"kernel library '{self.name}' has no function {func}") from e
+            f.restype = ctypes.c_int
+            self._funcs[func] = f
+        rc = f(*args)
+        if rc != 0:
+            raise KernelError(self.lib.bfi_last_error().decode("utf-8", "replace"))
+
+
+def library(name: str) -> KernelLibrary:
+    lib = _loaded.get(name)
+    if lib is None:
+        with _lock:
+            lib = _loaded.get(name)
+            if lib is None:
+                lib = KernelLibrary(name)
+                _loaded[name] = lib
+    return lib

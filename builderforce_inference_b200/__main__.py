@@ -1,0 +1,160 @@
+"""Command line, in the manner of the reference's ``bfi`` (crates/bfi/src/cli.rs:31-125):
+
+    python -m builderforce_inference_b200 run   <model> [prompt]      one-shot, or a prompt loop without [prompt]
+    python -m builderforce_inference_b200 bench <model> --pp 512 --tg 128
+    python -m builderforce_inference_b200 random <config.json> <folder> --seed N
+
+``<model>`` is a folder with config.json and model.safetensors.  A prompt is a list of token ids
+separated by spaces or commas (tokenizers are outside this library); generated ids are printed
+the same way.  ``run`` samples with the reference's defaults (greedy, 256 tokens:
+crates/bfi/src/commands.rs:79, crates/bfi-runtime/src/sample.rs:33-49) unless told otherwise.
+``bench`` reports ``pp{N}`` and ``tg{N}`` tokens per second as a table
+(crates/bfi/src/commands.rs:250-294), timed on the device after a warm-up.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import re
+import sys
+import time
+
+
+def _ids(text: str):
+    parts = [p for p in re.split(r"[,\s]+", text.strip()) if p]
+    try:
+        return [int(p) for p in parts]
+    except ValueError:
+        raise SystemExit(f"a prompt is a list of token ids, got {text!r}")
+
+
+def _engine_flags(p: argparse.ArgumentParser) -> None:
+    p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    p.add_argument("--max-seq-len", type=int, default=None, help="cap on one sequence's context")
+    p.add_argument("--max-tokens-cached", type=int, default=65536,
+                   help="tokens the cache holds over all live sequences")
+    p.add_argument("--max-batch", type=int, default=64)
+    p.add_argument("--device", default="cuda:0")
+
+
+def _sample_flags(p: argparse.ArgumentParser) -> None:
+    p.add_argument("--max-tokens", type=int, default=256, help="0: until the context is full")
+    p.add_argument("--temperature", type=float, default=0.0, help="0: greedy")
+    p.add_argument("--top-k", type=int, default=0)
+    p.add_argument("--top-p", type=float, default=1.0)
+    p.add_argument("--min-p", type=float, default=0.0)
+    p.add_argument("--repeat-penalty", type=float, default=1.0)
+    p.add_argument("--presence-penalty", type=float, default=0.0)
+    p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--stop-id", type=int, action="append", default=None,
+                   help="stop token id (repeatable); default: eos_token_id of config.json")
+    p.add_argument("--ignore-eos", action="store_true")
+
+
+def _params(a):
+    from .sampling import SampleParams
+    return SampleParams(max_tokens=a.max_tokens, temperature=a.temperature, top_k=a.top_k, top_p=a.top_p,
+                        min_p=a.min_p, repeat_penalty=a.repeat_penalty, presence_penalty=a.presence_penalty,
+                        seed=a.seed)
+
+
+def _load(a):
+    from .engine.api import Model
+    print(f"loading {a.model}", file=sys.stderr, flush=True)
+    return Model.load(a.model, dtype=a.dtype, max_tokens=a.max_tokens_cached, max_seq_len=a.max_seq_len,
+                      max_batch=a.max_batch, device=a.device)
+
+
+def cmd_run(a) -> int:
+    model = _load(a)
+    params = _params(a)
+    if a.prompt is not None:
+        out = model.generate(_ids(a.prompt), params, a.stop_id, a.ignore_eos)
+        print(" ".join(str(t) for t in out))
+        return 0
+    print("token ids per line; an empty line, /bye or /exit quits", file=sys.stderr)
+    while True:
+        sys.stdout.write("> ")
+        sys.stdout.flush()
+        line = sys.stdin.readline()
+        if not line:
+            break
+        t = line.strip()
+        if not t or t in ("/bye", "/exit"):
+            break
+        out = model.generate(_ids(t), params, a.stop_id, a.ignore_eos)
+        print(" ".join(str(x) for x in out))
+    return 0
+
+
+def cmd_bench(a) -> int:
+    import torch
+    from .sampling import SampleParams
+    model = _load(a)
+    vocab = model.n_vocab()
+    g = torch.Generator().manual_seed(0)
+    pp_prompt = torch.randint(0, vocab, (max(a.pp, 1),), generator=g).tolist()
+    tg_prompt = torch.randint(0, vocab, (2,), generator=g).tolist()
+
+    def timed(prompt, n_new):
+        model.generate(prompt, SampleParams(max_tokens=n_new), ignore_eos=True)       # warm-up
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        model.generate(prompt, SampleParams(max_tokens=n_new), ignore_eos=True)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 1e3
+
+    pp_s = timed(pp_prompt, 1)
+    tg_s = timed(tg_prompt, a.tg)
+    label = f"B200 sm_100a {a.dtype}"
+    rows = [("pp%d" % a.pp, a.pp / pp_s), ("tg%d" % a.tg, a.tg / tg_s)]
+    if a.json:
+        print(json.dumps({name: ts for name, ts in rows}))
+        return 0
+    print("| model | backend | test | t/s |")
+    print("|---|---|---|---|")
+    for name, ts in rows:
+        print(f"| {a.model} | {label} | {name} | {ts:.2f} |")
+    return 0
+
+
+def cmd_random(a) -> int:
+    import torch
+    from .config import read_json
+    from .weights import write_model_folder
+    dt = {"bfloat16": torch.bfloat16, "float32": torch.float32}[a.store_dtype]
+    write_model_folder(read_json(a.config), a.seed, a.folder, dt)
+    print(a.folder)
+    return 0
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="builderforce_inference_b200", description=__doc__,
+                                 formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    r = sub.add_parser("run", help="generate for one prompt, or read prompts line by line")
+    r.add_argument("model")
+    r.add_argument("prompt", nargs="?", default=None)
+    _engine_flags(r)
+    _sample_flags(r)
+    r.set_defaults(fn=cmd_run)
+    b = sub.add_parser("bench", help="pp/tg tokens per second")
+    b.add_argument("model")
+    b.add_argument("--pp", type=int, default=512)
+    b.add_argument("--tg", type=int, default=128)
+    b.add_argument("--json", action="store_true")
+    _engine_flags(b)
+    b.set_defaults(fn=cmd_bench)
+    w = sub.add_parser("random", help="write a model folder with random weights")
+    w.add_argument("config")
+    w.add_argument("folder")
+    w.add_argument("--seed", type=int, default=0)
+    w.add_argument("--store-dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    w.set_defaults(fn=cmd_random)
+    a = ap.parse_args(argv)
+    return a.fn(a)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -117,7 +117,7 @@ class Engine:
         self.use_graphs = bool(use_graphs) and self.decoder.graph_safe()
         self._graphs: Dict[int, _DecodeGraph] = {}
         self._pinned: Dict[int, torch.Tensor] = {}
-        self.kernel_launches = 0       # steps' kernels are counted by the benchmark through this hook
+        self.last_h2d_bytes = 0        # bytes of index arrays the last step copied to the device
 
     # ---- construction ----------------------------------------------------------------
     @classmethod
@@ -340,6 +340,7 @@ class Engine:
             torch.cuda.current_stream(self.device).synchronize()
         pinned.copy_(torch.tensor(host, dtype=torch.int32))
         meta[:n].copy_(pinned, non_blocking=True)
+        self.last_h2d_bytes = 4 * n
 
     def _context_from_meta(self, meta, n_tok, n_seq, max_seq_tokens, host) -> StepContext:
         ids, pos, slot_of, cu, seq_slot, seq_start, _ = self._meta_slices(meta, n_tok, n_seq, 0)

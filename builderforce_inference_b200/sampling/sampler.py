@@ -1,0 +1,129 @@
+"""Choosing next tokens on the device.
+
+Greedy, temperature, penalties and min-p run in this package's kernels (``sample_rows``,
+``argmax_rows``).  Top-k and top-p, which need the probabilities in descending order
+(crates/bfi-runtime/src/sample.rs:392-409), sort with the tensor library and then draw exactly as
+the reference does: in list order, which after a sort is descending probability.
+
+The uniform number of a draw depends on (seed, request index, step), so a run is reproducible
+and every step and request draws its own number.  The reference restarts its generator from the
+seed at every call (sample.rs:304-309), which hands every step the same number; the generator's
+update and its map to [0, 1) are kept (sample.rs:442-460).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..kernels import ops
+from .params import SampleParams
+
+_MASK = (1 << 64) - 1
+
+
+def uniform_draw(seed: int, request: int, step: int) -> float:
+    """A number in [0, 1) for one draw: a 64-bit mix of the three counters, then one step of the
+    reference's xorshift (13, 7, 17) and its ``(x >> 40) / 2^24``."""
+    x = (seed * 0x9E3779B97F4A7C15 + request * 0xBF58476D1CE4E5B9 + step * 0x94D049BB133111EB + 0x2545F4914F6CDD1D) & _MASK
+    x ^= x >> 30
+    x = (x * 0xBF58476D1CE4E5B9) & _MASK
+    x ^= x >> 27
+    x = (x * 0x94D049BB133111EB) & _MASK
+    x ^= x >> 31
+    if x == 0:
+        x = 0x9E3779B97F4A7C15
+    x ^= (x << 13) & _MASK
+    x ^= x >> 7
+    x ^= (x << 17) & _MASK
+    return float(x >> 40) / float(1 << 24)
+
+
+class Sampler:
+    """Holds the small device buffers sampling needs."""
+
+    def __init__(self, device: torch.device, vocab_size: int):
+        self.device = device
+        self.vocab = vocab_size
+        self._out = torch.empty(0, dtype=torch.int32, device=device)
+        self._work: Optional[torch.Tensor] = None
+
+    def _out_rows(self, n: int) -> torch.Tensor:
+        if self._out.numel() < n:
+            self._out = torch.empty(max(n, 2 * self._out.numel()), dtype=torch.int32, device=self.device)
+        return self._out[:n]
+
+    def sample(self, logits: torch.Tensor, params: SampleParams, requests: Sequence[int], steps: Sequence[int],
+               histories: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+        """``logits`` float32 ``[rows, vocab]`` on the device; returns int32 ids ``[rows]`` on the
+        device.  ``histories[i]`` (prompt + generated so far) is needed only with penalties."""
+        rows = logits.shape[0]
+        out = self._out_rows(rows)
+        if rows == 0:
+            return out
+        if params.greedy and not params.has_penalties:
+            ops.argmax_rows(logits, out)
+            return out
+        u = [uniform_draw(params.seed, r, s) for r, s in zip(requests, steps)]
+        seen = seen_cu = work = None
+        if params.has_penalties:
+            if histories is None:
+                raise ValueError("penalties need the token history of every row")
+            flat: List[int] = []
+            cu = [0]
+            for h in histories:
+                uniq = sorted({int(t) for t in h if 0 <= int(t) < self.vocab})
+                flat.extend(uniq)
+                cu.append(len(flat))
+            if flat:
+                seen = torch.tensor(flat, dtype=torch.int32, device=self.device)
+                seen_cu = torch.tensor(cu, dtype=torch.int32, device=self.device)
+                if self._work is None or self._work.numel() < rows * self.vocab:
+                    self._work = torch.empty(rows * self.vocab, dtype=torch.float32, device=self.device)
+                work = self._work
+        if params.needs_sort:
+            return self._sample_sorted(logits, params, u, seen, seen_cu, out)
+        temp = torch.full((rows,), float(params.temperature), dtype=torch.float32, device=self.device)
+        ut = torch.tensor(u, dtype=torch.float32, device=self.device)
+        ops.sample_rows(logits, temp, ut, out, params.repeat_penalty, params.presence_penalty, params.min_p,
+                        seen, seen_cu, work)
+        return out
+
+    def _sample_sorted(self, logits, params: SampleParams, u, seen, seen_cu, out) -> torch.Tensor:
+        """Top-k / top-p: penalties, softmax, descending sort, cuts, min-p, draw in sorted order."""
+        x = logits.clone()
+        if seen is not None:
+            cu = seen_cu.tolist()
+            for r in range(x.shape[0]):
+                ids = seen[cu[r]:cu[r + 1]].long()
+                if ids.numel() == 0:
+                    continue
+                v = x[r, ids]
+                if abs(params.repeat_penalty - 1.0) > 1.1920929e-07:
+                    v = torch.where(v > 0, v / params.repeat_penalty, v * params.repeat_penalty)
+                x[r, ids] = v - params.presence_penalty
+        x = x / params.temperature
+        p = torch.softmax(x, dim=-1)
+        sp, si = torch.sort(p, dim=-1, descending=True, stable=True)
+        keep = torch.ones_like(sp, dtype=torch.bool)
+        if params.top_k > 0 and params.top_k < sp.shape[1]:
+            keep[:, params.top_k:] = False
+        if params.top_p < 1.0:
+            cum = torch.cumsum(sp * keep, dim=-1)
+            # keep through the first position whose running sum reaches top_p (at least one)
+            before = cum - sp * keep
+            keep &= before < params.top_p
+            keep[:, 0] = True
+        if params.min_p > 0.0:
+            keep &= sp >= params.min_p * sp[:, :1]
+        w = sp * keep
+        total = w.sum(dim=-1, keepdim=True)
+        r = torch.tensor(u, dtype=torch.float32, device=logits.device)[:, None] * total
+        cumw = torch.cumsum(w, dim=-1)
+        hit = (cumw >= r) & keep
+        first = torch.argmax(hit.int(), dim=-1)
+        none = ~hit.any(dim=-1)
+        last_kept = keep.int().cumsum(dim=-1).argmax(dim=-1)
+        first = torch.where(none, last_kept, first)
+        out.copy_(si.gather(1, first[:, None]).squeeze(1).to(torch.int32))
+        return out

@@ -1,0 +1,194 @@
+"""The cache's bookkeeping on the CPU: no slot or page lost, held twice or freed twice; reuse;
+windows; limits; fixed-size state beside the pages."""
+import random
+
+import pytest
+import torch
+
+from builderforce_inference_b200.cache import PAGE_TOKENS, CacheError, FreeList, PageTable, SequenceCache
+from builderforce_inference_b200.parts.base import KVNeed, StateNeed
+
+CPU = torch.device("cpu")
+
+
+def make(needs=None, cache_of=None, max_tokens=64 * 8, max_seq_len=256, slots=4):
+    needs = needs if needs is not None else [KVNeed(2, 16), KVNeed(2, 16)]
+    cache_of = cache_of if cache_of is not None else [None] * len(needs)
+    return SequenceCache(needs, cache_of, max_tokens, max_seq_len, torch.float32, CPU, initial_slots=slots)
+
+
+def test_free_list_lowest_first_and_double_free():
+    f = FreeList(3, "slot")
+    assert [f.take(), f.take(), f.take()] == [0, 1, 2]
+    with pytest.raises(CacheError, match="no free slot"):
+        f.take()
+    f.give_back(1)
+    f.give_back(0)
+    with pytest.raises(CacheError, match="not held"):
+        f.give_back(1)
+    assert f.take() == 0 and f.take() == 1
+    f.check()
+
+
+def test_slots_are_given_back_and_used_again():
+    c = make()
+    a, b = c.acquire(), c.acquire()
+    c.begin_step([a, b], [70, 3]); c.end_step([a, b], [70, 3])
+    assert c.length(a) == 70 and c.length(b) == 3
+    g = c.kv_groups[0]
+    assert g.table.held_pages() == 3
+    c.release(a)
+    with pytest.raises(CacheError):
+        c.release(a)                       # freed twice
+    with pytest.raises(CacheError):
+        c.begin_step([a], [1])             # not held
+    a2 = c.acquire()
+    assert a2 == a and c.length(a2) == 0   # same slot again, empty
+    assert g.table.held_pages() == 1
+    c.begin_step([a2], [1]); c.end_step([a2], [1])
+    assert g.table.held_pages() == 2
+    assert g.block_host[a2, 0] >= 0 and g.block_host[a2, 1] == -1
+    c.check()
+
+
+def test_pages_grow_with_length_and_block_table_mirrors_them():
+    c = make()
+    s = c.acquire()
+    g = c.kv_groups[0]
+    c.begin_step([s], [64]); c.end_step([s], [64])
+    assert g.table.held_pages() == 1
+    c.begin_step([s], [1])                 # position 64 needs the second page
+    assert g.table.held_pages() == 2
+    c.end_step([s], [1])
+    row = g.table.rows[s]
+    assert g.block_dev[s, :2].tolist() == row and g.block_dev[s, 2].item() == -1
+    c.check()
+
+
+def test_limits_are_refused_before_anything_changes():
+    c = make(max_tokens=64 * 3, max_seq_len=128)
+    a, b = c.acquire(), c.acquire()
+    with pytest.raises(CacheError, match="context_exceeded"):
+        c.begin_step([a], [129])
+    with pytest.raises(CacheError, match="twice"):
+        c.begin_step([a, a], [1, 1])
+    with pytest.raises(CacheError, match="at least one"):
+        c.begin_step([a], [0])
+    c.begin_step([a], [128]); c.end_step([a], [128])      # two pages
+    with pytest.raises(CacheError, match="cache full"):
+        c.begin_step([b], [65])                            # needs two, one is free
+    assert c.kv_groups[0].table.held_pages() == 2 and c.length(b) == 0
+    c.begin_step([b], [64]); c.end_step([b], [64])
+    with pytest.raises(CacheError, match="context_exceeded"):
+        c.begin_step([a], [1])
+    c.check()
+
+
+def test_slot_table_grows_up_to_the_page_count():
+    c = make(max_tokens=64 * 6, slots=2)
+    got = [c.acquire() for _ in range(6)]
+    assert got == list(range(6)) and c.n_slots >= 6 and c.generation > 0
+    with pytest.raises(CacheError, match="no free slot"):
+        c.acquire()
+    for s in got:
+        c.release(s)
+    c.check()
+
+
+def test_window_group_lets_go_of_pages_behind_the_window():
+    c = make(needs=[KVNeed(1, 16), KVNeed(1, 16, window=40)], max_tokens=64 * 16, max_seq_len=1024)
+    full, win = c.kv_groups
+    assert full.need.window is None and win.need.window == 40
+    s = c.acquire()
+    c.begin_step([s], [200])
+    assert win.table.held_pages() == 4         # the whole prompt is present during its step
+    c.end_step([s], [200])
+    # next token is at 200; it reads keys 161..200: blocks 2 and 3
+    assert full.table.held_pages() == 4 and win.table.held_pages() == 2
+    assert win.block_host[s, :4].tolist()[:2] == [-1, -1]
+    for _ in range(60):
+        c.begin_step([s], [1]); c.end_step([s], [1])
+    # length 260: next token at 260 reads 221..260 -> blocks 3 and 4
+    assert win.table.held_pages() == 2 and full.table.held_pages() == 5
+    assert c.live_kv_bytes() == 260 * full.bytes_per_token() + 39 * win.bytes_per_token()
+    c.release(s)
+    assert win.table.held_pages() == 0 and full.table.held_pages() == 0
+    c.check()
+
+
+def test_groups_and_shared_caches():
+    needs = [KVNeed(2, 16), KVNeed(2, 16), KVNeed(2, 16, window=8), StateNeed((3, 5)), None, KVNeed(2, 16)]
+    cache_of = [None, None, None, None, None, 1]
+    c = make(needs=needs, cache_of=cache_of)
+    assert [g.runs for g in c.kv_groups] == [[0, 1], [2]]
+    assert [g.runs for g in c.state_groups] == [[3]]
+    r1, r5 = c.run_cache(1), c.run_cache(5)
+    assert r5.kv.k.data_ptr() == r1.kv.k.data_ptr() and r1.writes_cache and not r5.writes_cache
+    assert c.run_cache(4).kv is None and c.run_cache(4).state is None
+    assert c.run_cache(3).state.shape[1:] == (3, 5)
+    with pytest.raises(CacheError):
+        make(needs=[KVNeed(2, 16), KVNeed(2, 16)], cache_of=[None, 1])
+    assert c.bytes_per_token() == (2 + 1) * 2 * 2 * 16 * 4          # kv_plan.rs:49-51 per group
+    assert c.state_bytes_per_slot() == 3 * 5 * 4
+
+
+def test_fixed_state_is_per_slot_and_reset_on_acquire():
+    c = make(needs=[StateNeed((4,)), KVNeed(1, 16)], slots=2)
+    a = c.acquire()
+    st = c.run_cache(0).state
+    st[a] += 3.0
+    b = c.acquire()
+    assert st[b].abs().sum() == 0 and st[a].sum() == 12.0
+    c.release(a)
+    a2 = c.acquire()
+    assert a2 == a and c.run_cache(0).state[a2].abs().sum() == 0
+    # growing the slot table keeps live state
+    c.run_cache(0).state[b] += 1.0
+    more = [c.acquire() for _ in range(3)]
+    assert c.run_cache(0).state[b].sum() == 4.0
+    for s in more + [a2, b]:
+        c.release(s)
+    c.check()
+
+
+def test_random_traffic_never_loses_or_duplicates_anything():
+    rng = random.Random(0)
+    c = make(needs=[KVNeed(1, 16), KVNeed(1, 16, window=70)], max_tokens=64 * 24, max_seq_len=512, slots=2)
+    live = {}
+    for it in range(600):
+        r = rng.random()
+        if r < 0.25 and len(live) < 8:
+            try:
+                s = c.acquire()
+                live[s] = 0
+            except CacheError:
+                pass
+        elif r < 0.45 and live:
+            s = rng.choice(list(live))
+            c.release(s)
+            del live[s]
+        elif live:
+            batch = rng.sample(list(live), rng.randint(1, len(live)))
+            counts = [rng.choice([1, 1, 1, 5, 64, 100]) for _ in batch]
+            try:
+                c.begin_step(batch, counts)
+            except CacheError as e:
+                assert "context_exceeded" in str(e) or "cache full" in str(e)
+                continue
+            c.end_step(batch, counts)
+            for s, n in zip(batch, counts):
+                live[s] += n
+        c.check()
+        assert {s: c.length(s) for s in live} == live
+        for g in c.kv_groups:
+            for s, n in live.items():
+                row = g.table.rows[s]
+                first = g.table.first_kept_position(n) // PAGE_TOKENS
+                for blk in range((n + PAGE_TOKENS - 1) // PAGE_TOKENS):
+                    assert (row[blk] >= 0) == (blk >= first), (g.need, s, n, blk, row)
+                assert g.block_host[s, :len(row)].tolist() == row
+    for s in list(live):
+        c.release(s)
+    for g in c.kv_groups:
+        assert g.table.held_pages() == 0 and g.table.pool.n_free == g.table.pool.capacity
+    assert c.slots.n_held == 0

@@ -1,0 +1,167 @@
+"""Decisions of the generation loop, on the CPU, against a toy stepper whose next token is a
+function of the whole history of its sequence (as crates/bfi-runtime/src/engine/decode_tests.rs
+does): a mixed-up slot, a lost token or a wrong step shows as a different output."""
+import pytest
+
+from builderforce_inference_b200.engine.generate import generate_batch, plan_batches, token_budget
+from builderforce_inference_b200.sampling import SampleParams, uniform_draw
+
+VOCAB = 50
+
+
+def next_token(history):
+    h = 17
+    for t in history:
+        h = (h * 31 + t + 1) % 1000003
+    return h % VOCAB
+
+
+def expected(prompt, budget, stop=()):
+    out, hist = [], list(prompt)
+    while len(out) < budget:
+        t = next_token(hist)
+        if t in stop:
+            return out, "stop"
+        out.append(t)
+        hist.append(t)
+    return out, "length"
+
+
+class ToyStepper:
+    page_tokens = 64
+
+    def __init__(self, max_seq_len=256, n_pages=64, n_slots=4):
+        self.max_seq_len, self.n_pages = max_seq_len, n_pages
+        self.free = list(range(n_slots - 1, -1, -1))
+        self.hist = {}
+        self.log = []            # ("prefill", n_seqs) / ("decode", n_seqs)
+        self.max_live = 0
+
+    def acquire(self):
+        s = self.free.pop()
+        self.hist[s] = []
+        self.max_live = max(self.max_live, len(self.hist))
+        return s
+
+    def release(self, slot):
+        assert slot in self.hist, "slot released twice"
+        del self.hist[slot]
+        self.free.append(slot)
+
+    def prefill(self, slots, prompts):
+        self.log.append(("prefill", len(slots)))
+        for s, p in zip(slots, prompts):
+            assert self.hist[s] == [], "slot not empty at prefill"
+            self.hist[s] = list(p)
+        return list(slots)
+
+    def decode(self, slots, tokens):
+        self.log.append(("decode", len(slots)))
+        for s, t in zip(slots, tokens):
+            self.hist[s].append(t)
+            assert len(self.hist[s]) <= self.max_seq_len
+        return list(slots)
+
+    def sample(self, handle, params, requests, steps, histories):
+        return [next_token(self.hist[s]) for s in handle]
+
+
+def test_budget_rules():
+    assert token_budget(10, 5, 100) == 5
+    assert token_budget(10, 0, 100) == 90            # 0: what the context still holds (mod.rs:353-357)
+    assert token_budget(98, 5, 100) == 2
+    assert token_budget(100, 5, 100) == 0
+    with pytest.raises(ValueError, match="context_exceeded"):
+        token_budget(101, 5, 100)
+
+
+def test_unequal_prompts_share_steps_and_shorter_ones_end_earlier():
+    st = ToyStepper(n_slots=4)
+    prompts = [[1, 2, 3], [4], [5, 6, 7, 8, 9], [10, 11]]
+    # budgets differ through the context limit: max_seq_len 12 -> 9, 11, 7, 10; cap by max_tokens 8
+    st.max_seq_len = 12
+    rep = generate_batch(st, prompts, SampleParams(max_tokens=8), max_batch=4)
+    want = [expected(p, min(8, 12 - len(p))) for p in prompts]
+    assert [(r.tokens, r.finish_reason) for r in rep.results] == want
+    # one prefill for all four; shared steps = the longest sequence's, not the sum (mod.rs:664-691)
+    assert st.log[0] == ("prefill", 4)
+    assert rep.shared_steps == 7 and len(st.log) == 8
+    assert [n for k, n in st.log[1:]] == [4, 4, 4, 4, 4, 4, 3]
+    assert st.hist == {} and sorted(st.free) == [0, 1, 2, 3]
+    assert rep.generated_tokens == sum(len(w[0]) for w in want)
+
+
+def test_stop_token_is_not_appended_and_frees_the_slot_at_once():
+    prompts = [[3, 1, 4], [1, 5, 9, 2], [6, 5]]
+    free_run = [expected(p, 12)[0] for p in prompts]
+    stop = {free_run[0][4], free_run[2][0]}
+    st = ToyStepper()
+    rep = generate_batch(st, prompts, SampleParams(max_tokens=12), stop_ids=stop, max_batch=3)
+    for p, r in zip(prompts, rep.results):
+        toks, why = expected(p, 12, stop)
+        assert (r.tokens, r.finish_reason) == (toks, why)
+        assert not set(r.tokens) & stop
+    assert rep.results[2].tokens == [] and rep.results[2].finish_reason == "stop"
+    assert st.log[1] == ("decode", 2)              # the third request never takes a decode step
+    assert st.hist == {}
+
+
+def test_the_last_token_is_not_forwarded():
+    st = ToyStepper()
+    rep = generate_batch(st, [[1, 2]], SampleParams(max_tokens=3))
+    assert len(rep.results[0].tokens) == 3
+    assert st.log == [("prefill", 1), ("decode", 1), ("decode", 1)]
+    st = ToyStepper()
+    rep = generate_batch(st, [[1, 2]], SampleParams(max_tokens=1))
+    assert st.log == [("prefill", 1)] and rep.shared_steps == 0
+
+
+def test_batches_follow_one_another_and_reuse_slots():
+    st = ToyStepper(n_slots=2)
+    prompts = [[i + 1, i + 2] for i in range(5)]
+    rep = generate_batch(st, prompts, SampleParams(max_tokens=4), max_batch=2)
+    assert rep.batches == 3 and st.max_live == 2
+    assert [k for k, _ in st.log if k == "prefill"] == ["prefill"] * 3
+    assert [r.tokens for r in rep.results] == [expected(p, 4)[0] for p in prompts]
+
+
+def test_batches_respect_the_cache_size():
+    # each request may hold 10 + 99 tokens -> 2 pages; 5 pages fit two requests
+    assert plan_batches([10] * 5, [100] * 5, max_batch=64, page_tokens=64, n_pages=5) == [[0, 1], [2, 3], [4]]
+    assert plan_batches([10, 200, 10], [10, 10, 10], 64, 64, 4) == [[0], [1], [2]]
+    with pytest.raises(ValueError, match="cache pages"):
+        plan_batches([1000], [10], 64, 64, 4)
+
+
+def test_full_context_and_empty_prompt():
+    st = ToyStepper(max_seq_len=8)
+    rep = generate_batch(st, [[1] * 8, [2] * 6], SampleParams(max_tokens=0))
+    assert rep.results[0].tokens == [] and rep.results[0].finish_reason == "length"
+    assert rep.results[1].tokens == expected([2] * 6, 2)[0]
+    assert st.log[0] == ("prefill", 1)
+    with pytest.raises(ValueError, match="empty prompt"):
+        generate_batch(ToyStepper(), [[]], SampleParams())
+    with pytest.raises(ValueError, match="context_exceeded"):
+        generate_batch(ToyStepper(max_seq_len=4), [[1] * 5], SampleParams())
+
+
+def test_slots_are_released_when_a_step_fails():
+    class Failing(ToyStepper):
+        def decode(self, slots, tokens):
+            raise RuntimeError("boom")
+    st = Failing()
+    with pytest.raises(RuntimeError, match="boom"):
+        generate_batch(st, [[1], [2]], SampleParams(max_tokens=5))
+    assert st.hist == {}
+
+
+def test_sample_params_and_draws():
+    SampleParams().validate()
+    assert SampleParams().max_tokens == 256 and SampleParams().greedy       # sample.rs:33-49
+    for bad in (dict(max_tokens=-1), dict(repeat_penalty=0.0), dict(top_p=0.0), dict(min_p=1.5), dict(top_k=-1)):
+        with pytest.raises(ValueError):
+            SampleParams(**bad).validate()
+    us = [uniform_draw(3, r, s) for r in range(4) for s in range(50)]
+    assert all(0.0 <= u < 1.0 for u in us) and len(set(us)) == len(us)
+    assert uniform_draw(3, 1, 2) == uniform_draw(3, 1, 2) != uniform_draw(4, 1, 2)
+    assert abs(sum(us) / len(us) - 0.5) < 0.1

@@ -38,6 +38,7 @@ class EngineStepper:
         self.sampler = Sampler(engine.device, engine.spec.vocab_size)
         self._host_ids = torch.empty(1024, dtype=torch.int32, pin_memory=True)
         self.last_logits: Optional[torch.Tensor] = None
+        self.on_tokens = None          # called with the number of ids after each read-back
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
@@ -67,6 +68,8 @@ class EngineStepper:
         host.copy_(ids, non_blocking=True)
         torch.cuda.current_stream(self.engine.device).synchronize()
         self.d2h_bytes = n * 4
+        if self.on_tokens is not None:
+            self.on_tokens(n)
         return host.tolist()
 
 

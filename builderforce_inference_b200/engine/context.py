@@ -70,3 +70,32 @@ class StepContext:
              n_rows: Optional[int] = None) -> torch.Tensor:
         return self.workspace.rows(tag, self.n_tokens if n_rows is None else n_rows, n_cols,
                                    dtype or self.act_dtype)
+
+
+def build_context(seqs, act_dtype: torch.dtype, workspace: Workspace, device,
+                  status: Optional[torch.Tensor] = None) -> StepContext:
+    """A context for ``seqs = [(slot, start, tokens), ...]``: each sequence brings ``tokens`` at
+    positions ``start, start+1, ...``.  Plain and unhurried; the engine packs its own arrays in one
+    transfer, this is for driving a part alone."""
+    ids: List[int] = []
+    pos: List[int] = []
+    slot_of: List[int] = []
+    cu = [0]
+    for slot, start, tokens in seqs:
+        ids += [int(t) for t in tokens]
+        pos += list(range(start, start + len(tokens)))
+        slot_of += [slot] * len(tokens)
+        cu.append(len(ids))
+
+    def i32(xs):
+        return torch.tensor(xs, dtype=torch.int32, device=device)
+
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=device)
+    return StepContext(
+        n_tokens=len(ids), n_seqs=len(seqs), max_seq_tokens=max(len(t) for _, _, t in seqs),
+        act_dtype=act_dtype, workspace=workspace, token_ids=i32(ids), token_pos=i32(pos),
+        token_slot=i32(slot_of), cu_seqlens=i32(cu), seq_slot=i32([s for s, _, _ in seqs]),
+        seq_start=i32([st for _, st, _ in seqs]), status=status,
+        host_seq_slot=[s for s, _, _ in seqs], host_seq_start=[st for _, st, _ in seqs],
+        host_seq_tokens=[len(t) for _, _, t in seqs])

@@ -26,6 +26,7 @@ from ..cache.cache import SequenceCache
 from ..cache.pages import PAGE_TOKENS, CacheError
 from ..config.base import ConfigError, read_json
 from ..kernels import ops
+from ..kernels.library import total_calls
 from ..parts.base import ModelSpec
 from ..registry import describe_model
 from ..weights.loader import load_folder
@@ -86,8 +87,10 @@ class _DecodeGraph:
             ctx = engine._context_from_meta(self.meta, batch, batch, 1, None)
         ctx.capturing = True
         self.graph = torch.cuda.CUDAGraph()
+        before = total_calls()
         with torch.cuda.graph(self.graph):
             engine._forward(ctx, self.rows, self.logits)
+        self.n_kernels = total_calls() - before      # launches one replay stands for
 
 
 class Engine:
@@ -118,6 +121,7 @@ class Engine:
         self._graphs: Dict[int, _DecodeGraph] = {}
         self._pinned: Dict[int, torch.Tensor] = {}
         self.last_h2d_bytes = 0        # bytes of index arrays the last step copied to the device
+        self.graph_kernel_launches = 0  # kernels launched through graph replays so far
 
     # ---- construction ----------------------------------------------------------------
     @classmethod
@@ -219,6 +223,7 @@ class Engine:
                 self._graphs[padded] = g
             self._fill_meta(g.meta, tokens, starts, slots, list(range(b + 1)), padded, padded)
             g.graph.replay()
+            self.graph_kernel_launches += g.n_kernels
             logits = g.logits
         else:
             meta = self._meta_buffer(b, b, 0)
@@ -356,6 +361,10 @@ class Engine:
         return (self.workspace.generation, self.cache.generation)
 
     # ---- accounting ------------------------------------------------------------------
+    def kernel_launches(self) -> int:
+        """Kernels of this package launched so far, directly or through graph replays."""
+        return total_calls() + self.graph_kernel_launches
+
     def decode_step_bytes(self) -> int:
         """Bytes a single-token step has to read: every weight once and the live sequences' cache."""
         return self.decoder.n_weight_bytes + self.cache.live_kv_bytes()

@@ -33,6 +33,7 @@ class KernelLibrary:
         self.name = name
         self.lib.bfi_last_error.restype = ctypes.c_char_p
         self._funcs: Dict[str, ctypes._CFuncPtr] = {}
+        self.calls = 0          # exported functions called so far (each launches at least one kernel)
 
     def call(self, func: str, *args) -> None:
         f = self._funcs.get(func)
@@ -43,9 +44,19 @@ class KernelLibrary:
                 raise KernelError(f"kernel library '{self.name}' has no function {func}") from e
             f.restype = ctypes.c_int
             self._funcs[func] = f
+        self.calls += 1
         rc = f(*args)
         if rc != 0:
             raise KernelError(self.lib.bfi_last_error().decode("utf-8", "replace"))
+
+
+def total_calls() -> int:
+    """Calls into the kernel libraries so far, over all loaded libraries."""
+    return sum(lib.calls for lib in _loaded.values())
+
+
+def loaded_libraries() -> Dict[str, str]:
+    return {name: lib.path for name, lib in _loaded.items()}
 
 
 def library(name: str) -> KernelLibrary:

@@ -1,0 +1,287 @@
+"""The engine against the plain implementation, in float32 and bfloat16: each request alone and
+whole; with the last 32 tokens one by one; in batches of unequal lengths whose shorter requests
+end earlier, one batch after another so that slots and pages are used again; long decoding; the
+first tokens of a sequence; a poisoned cache; cut prompts; windows."""
+import pytest
+import torch
+
+from helpers import CONFIGS, model_folder, plain_logits, random_prompts, rel_err, store_dtype, tol
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+
+
+def load(name, dtype, **kw):
+    from builderforce_inference_b200.engine.engine import Engine
+    kw.setdefault("max_tokens", 4096)
+    return Engine.load(model_folder(name, store_dtype(dtype)), dtype=dtype, **kw)
+
+
+def S(slot, tokens, want):
+    from builderforce_inference_b200.engine.engine import SequenceStep
+    return SequenceStep(slot, tokens, want)
+
+
+def check(got, ref, dtype, what=""):
+    err = rel_err(got, ref)
+    assert err < tol(dtype), f"{what}: rel err {err:.3e} over {tol(dtype):.0e}"
+    return err
+
+
+def first_bad_row(got, ref, dtype):
+    for i in range(got.shape[0]):
+        if rel_err(got[i:i + 1], ref[i:i + 1]) >= tol(dtype):
+            return i
+    return None
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_each_request_alone_and_whole(name, dtype):
+    eng = load(name, dtype)
+    folder = model_folder(name, store_dtype(dtype))
+    lens = [1, 2, 5, 17, 33, 64, 65, 100]
+    for p in random_prompts(CONFIGS[name]["vocab_size"], lens):
+        s = eng.acquire()
+        got = eng.step([S(s, p, list(range(len(p))))]).cpu()
+        ref = plain_logits(folder, p)
+        assert got.shape == ref.shape
+        bad = first_bad_row(got, ref, dtype)
+        assert bad is None, f"len {len(p)}: first wrong position {bad}"
+        eng.release(s)
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_last_32_tokens_one_by_one(name, dtype, graphs):
+    eng = load(name, dtype, use_graphs=graphs)
+    folder = model_folder(name, store_dtype(dtype))
+    for p in random_prompts(CONFIGS[name]["vocab_size"], [33, 40, 96, 120], seed=8):
+        ref = plain_logits(folder, p)
+        k = len(p) - 32
+        s = eng.acquire()
+        rows = [eng.step([S(s, p[:k], list(range(k)))]).cpu().clone()]
+        for t in range(k, len(p)):
+            rows.append(eng.step([S(s, [p[t]], [0])]).cpu().clone())
+        got = torch.cat(rows)
+        bad = first_bad_row(got, ref, dtype)
+        assert bad is None, f"len {len(p)}: first wrong position {bad} (prompt end at {k})"
+        eng.release(s)
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_unequal_batches_one_after_another(name, dtype, graphs):
+    """Batches start together (one step with every prompt prefix), then one token each; shorter
+    requests end earlier and give their slot back; the next batch reuses slots and pages that
+    still hold the previous batch's rows."""
+    eng = load(name, dtype, use_graphs=graphs, max_tokens=64 * 12)
+    folder = model_folder(name, store_dtype(dtype))
+    vocab = CONFIGS[name]["vocab_size"]
+    batches = [[5, 11, 17], [1, 7, 32, 64], [100, 3], [70, 70, 2, 9, 31]]
+    seen_slots = []
+    for bi, lens in enumerate(batches):
+        prompts = random_prompts(vocab, lens, seed=20 + bi)
+        refs = [plain_logits(folder, p) for p in prompts]
+        n_pref = [max(1, n - 3 - 2 * i) for i, n in enumerate(lens)]
+        slots = [eng.acquire() for _ in prompts]
+        seen_slots.append(list(slots))
+        lg = eng.step([S(s, p[:k], list(range(k))) for s, p, k in zip(slots, prompts, n_pref)]).cpu().clone()
+        got = [[] for _ in prompts]
+        o = 0
+        for i, k in enumerate(n_pref):
+            got[i].append(lg[o:o + k])
+            o += k
+        pos = list(n_pref)
+        live = [i for i in range(len(prompts)) if pos[i] < lens[i]]
+        for i in range(len(prompts)):
+            if i not in live:
+                eng.release(slots[i])
+        while live:
+            lg = eng.step([S(slots[i], [prompts[i][pos[i]]], [0]) for i in live]).cpu().clone()
+            for j, i in enumerate(live):
+                got[i].append(lg[j:j + 1])
+                pos[i] += 1
+            for i in list(live):
+                if pos[i] == lens[i]:
+                    eng.release(slots[i])
+                    live.remove(i)
+        for i, ref in enumerate(refs):
+            g = torch.cat(got[i])
+            bad = first_bad_row(g, ref, dtype)
+            assert bad is None, f"batch {bi} request {i} (len {lens[i]}, prefix {n_pref[i]}): first wrong position {bad}"
+        eng.cache.check()
+        assert eng.cache.slots.n_held == 0
+    assert set(seen_slots[1]) & set(seen_slots[0]), "slots were not reused"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(dtype):
+    """Hundreds of single-token steps across many page edges, two sequences of different phase."""
+    name = "D"
+    eng = load(name, dtype)
+    folder = model_folder(name, store_dtype(dtype))
+    pa, pb = random_prompts(CONFIGS[name]["vocab_size"], [400, 333], seed=31)
+    ra, rb = plain_logits(folder, pa), plain_logits(folder, pb)
+    a, b = eng.acquire(), eng.acquire()
+    lg = eng.step([S(a, pa[:10], [9]), S(b, pb[:50], [49])]).cpu()
+    assert rel_err(lg[0:1], ra[9:10]) < tol(dtype) and rel_err(lg[1:2], rb[49:50]) < tol(dtype)
+    ia, ib = 10, 50
+    worst = 0.0
+    while ia < len(pa) or ib < len(pb):
+        seqs, who = [], []
+        if ia < len(pa):
+            seqs.append(S(a, [pa[ia]], [0])); who.append(("a", ia)); ia += 1
+        if ib < len(pb):
+            seqs.append(S(b, [pb[ib]], [0])); who.append(("b", ib)); ib += 1
+        lg = eng.step(seqs).cpu()
+        for j, (w, i) in enumerate(who):
+            ref = ra if w == "a" else rb
+            e = rel_err(lg[j:j + 1], ref[i:i + 1])
+            assert e < tol(dtype), f"sequence {w} position {i}: rel err {e:.3e}"
+            worst = max(worst, e)
+    eng.release(a)
+    eng.release(b)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_first_tokens_of_a_sequence(dtype):
+    """Position 0 and 1: a one-token prompt, then its first decoded tokens, alone and beside a
+    longer neighbour."""
+    name = "B"
+    eng = load(name, dtype)
+    folder = model_folder(name, store_dtype(dtype))
+    p, q = random_prompts(CONFIGS[name]["vocab_size"], [4, 40], seed=2)
+    ref, refq = plain_logits(folder, p), plain_logits(folder, q)
+    s = eng.acquire()
+    rows = [eng.step([S(s, [p[0]], [0])]).cpu().clone()]
+    for t in p[1:]:
+        rows.append(eng.step([S(s, [t], [0])]).cpu().clone())
+    check(torch.cat(rows), ref, dtype, "alone")
+    eng.release(s)
+    s, n = eng.acquire(), eng.acquire()
+    lg = eng.step([S(s, [p[0]], [0]), S(n, q[:37], [36])]).cpu().clone()
+    check(lg[0:1], ref[0:1], dtype, "position 0 beside a neighbour")
+    check(lg[1:2], refq[36:37], dtype, "neighbour")
+    for i in range(1, 4):
+        lg = eng.step([S(n, [q[36 + i]], [0]), S(s, [p[i]], [0])]).cpu().clone()
+        check(lg[1:2], ref[i:i + 1], dtype, f"position {i}")
+        check(lg[0:1], refq[36 + i:37 + i], dtype, f"neighbour {i}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_poisoned_cache_and_stale_rows_do_not_matter(dtype):
+    """Every page is filled with NaN before use: rows at or past a sequence's length, and rows a
+    freed slot left behind, are never read."""
+    name = "A"
+    eng = load(name, dtype, max_tokens=64 * 4)
+    folder = model_folder(name, store_dtype(dtype))
+    eng.cache.poison()
+    p1, p2 = random_prompts(CONFIGS[name]["vocab_size"], [70, 45], seed=4)
+    s = eng.acquire()
+    check(eng.step([S(s, p1, list(range(70)))]).cpu(), plain_logits(folder, p1), dtype, "first use")
+    eng.release(s)
+    s2 = eng.acquire()
+    assert s2 == s
+    got = [eng.step([S(s2, p2[:30], list(range(30)))]).cpu().clone()]
+    for t in p2[30:]:
+        got.append(eng.step([S(s2, [t], [0])]).cpu().clone())
+    check(torch.cat(got), plain_logits(folder, p2), dtype, "reused slot over stale rows")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_prompts_cut_into_pieces_give_the_same_logits(name, dtype):
+    """A step may continue a cached prefix with several tokens, and the engine itself cuts long
+    steps into micro-batches: neither changes a logit beyond rounding."""
+    folder = model_folder(name, store_dtype(dtype))
+    p, q = random_prompts(CONFIGS[name]["vocab_size"], [150, 90], seed=6)
+    rp, rq = plain_logits(folder, p), plain_logits(folder, q)
+    eng = load(name, dtype)
+    a, b = eng.acquire(), eng.acquire()
+    cuts_a, cuts_b = [0, 1, 64, 65, 130, 150], [0, 33, 34, 90]
+    ga, gb = [], []
+    for step in range(5):
+        seqs = []
+        if step + 1 < len(cuts_a):
+            ta = p[cuts_a[step]:cuts_a[step + 1]]
+            seqs.append(S(a, ta, list(range(len(ta)))))
+        if step + 1 < len(cuts_b):
+            tb = q[cuts_b[step]:cuts_b[step + 1]]
+            seqs.append(S(b, tb, list(range(len(tb)))))
+        lg = eng.step(seqs).cpu().clone()
+        if step + 1 < len(cuts_a):
+            ga.append(lg[:len(ta)])
+            lg = lg[len(ta):]
+        if step + 1 < len(cuts_b):
+            gb.append(lg)
+    check(torch.cat(ga), rp, dtype, "pieces, request a")
+    check(torch.cat(gb), rq, dtype, "pieces, request b")
+    small = load(name, dtype, prefill_chunk_tokens=64)
+    a, b = small.acquire(), small.acquire()
+    lg = small.step([S(a, p, list(range(150))), S(b, q, [89, 0, 45])]).cpu()
+    check(lg[:150], rp, dtype, "micro-batches, request a")
+    check(lg[150:], rq[[89, 0, 45]], dtype, "micro-batches, wanted places in the given order")
+
+
+def test_logits_do_not_depend_on_the_batch_or_the_slot():
+    """The same request alone, in a crowd, in another slot and through a padded captured step."""
+    name, dtype = "B", "float32"
+    folder = model_folder(name, store_dtype(dtype))
+    p = random_prompts(CONFIGS[name]["vocab_size"], [48], seed=9)[0]
+    others = random_prompts(CONFIGS[name]["vocab_size"], [5, 90, 64, 33, 12], seed=10)
+    outs = []
+    for crowd, graphs in ((0, False), (3, False), (5, True), (2, True)):
+        eng = load(name, dtype, use_graphs=graphs)
+        pre = [eng.acquire() for _ in range(crowd)]
+        s = eng.acquire()
+        seqs = [S(x, o[:-1], []) for x, o in zip(pre, others)] + [S(s, p[:40], [])]
+        assert eng.step(seqs).shape[0] == 0
+        rows = []
+        for i in range(40, 48):
+            seqs = [S(x, [o[-1]], []) for x, o in zip(pre[:crowd if i == 40 else 0], others)] + [S(s, [p[i]], [0])]
+            rows.append(eng.step(seqs).cpu().clone())
+        outs.append(torch.cat(rows))
+    ref = plain_logits(folder, p)[40:]
+    for o in outs:
+        assert rel_err(o, ref) < 1e-5
+        assert rel_err(o, outs[0]) < 2e-6
+
+
+def test_refusals_come_before_any_launch():
+    from builderforce_inference_b200.engine.engine import StepError
+    eng = load("A", "float32", max_tokens=128)
+    s = eng.acquire()
+    with pytest.raises(StepError, match="empty token list"):
+        eng.step([S(s, [], [])])
+    with pytest.raises(StepError, match="out of range"):
+        eng.step([S(s, [1, 256], [0])])
+    with pytest.raises(StepError, match="wanted place"):
+        eng.step([S(s, [1, 2], [2])])
+    with pytest.raises(StepError, match="context_exceeded"):
+        eng.step([S(s, [1] * 129, [0])])
+    with pytest.raises(StepError, match="not held"):
+        eng.step([S(s + 1, [1], [0])])
+    assert eng.length(s) == 0
+    eng.step([S(s, [1] * 128, [127])])
+    with pytest.raises(StepError, match="context_exceeded"):
+        eng.step([S(s, [1], [0])])
+    eng.release(s)
+    eng.cache.check()
+
+
+def test_a_32bit_checkpoint_runs_in_a_bfloat16_engine():
+    """A tensor stored in 32-bit stays so; the kernels take the mixed pair."""
+    name = "A"
+    folder = model_folder(name, torch.float32)
+    from builderforce_inference_b200.engine.engine import Engine
+    eng = Engine.load(folder, dtype="bfloat16", max_tokens=256)
+    assert eng.decoder.embedding.dtype == torch.float32
+    p = random_prompts(CONFIGS[name]["vocab_size"], [40])[0]
+    s = eng.acquire()
+    got = eng.step([S(s, p, list(range(40)))]).cpu()
+    assert rel_err(got, plain_logits(folder, p)) < tol("bfloat16")

@@ -1,0 +1,107 @@
+"""bin/trace_run as a user drives it: requests whole, with the last 32 tokens one by one, and in
+unequal batches one after another, in float32 and bfloat16, against the plain implementation."""
+import os
+
+import pytest
+import torch
+
+from helpers import CONFIGS, model_folder, plain_logits, random_prompts, rel_err, run_trace, store_dtype, tol
+
+pytestmark = pytest.mark.gpu
+
+
+def schedules(prompts):
+    """Three ways of cutting the same requests into steps; each returns (steps, where), where
+    ``where[(request, position)] = (step, row)``."""
+    out = {}
+    # 1. each request alone and whole
+    steps, where, n = [], {}, 0
+    for i, p in enumerate(prompts):
+        steps.append({"step": n, "entries": [{"id": f"r{i}", "tokens": p, "want": list(range(len(p)))}],
+                      "end": [f"r{i}"]})
+        for t in range(len(p)):
+            where[(i, t)] = (n, t)
+        n += 1
+    out["whole"] = (steps, where)
+    # 2. the last 32 tokens (or all but the first) one by one
+    steps, where, n = [], {}, 0
+    for i, p in enumerate(prompts):
+        k = max(1, len(p) - 32)
+        steps.append({"step": n, "entries": [{"id": f"r{i}", "tokens": p[:k], "want": list(range(k))}], "end": []})
+        for t in range(k):
+            where[(i, t)] = (n, t)
+        n += 1
+        for t in range(k, len(p)):
+            steps.append({"step": n, "entries": [{"id": f"r{i}", "tokens": [p[t]], "want": [0]}],
+                          "end": [f"r{i}"] if t == len(p) - 1 else []})
+            where[(i, t)] = (n, 0)
+            n += 1
+        if k == len(p):
+            steps[-1]["end"] = [f"r{i}"]
+    out["last32"] = (steps, where)
+    # 3. batches of three requests that start together; shorter ones end earlier; batches follow
+    steps, where, n = [], {}, 0
+    for b0 in range(0, len(prompts), 3):
+        group = list(range(b0, min(b0 + 3, len(prompts))))
+        pre = {i: max(1, len(prompts[i]) - 5 - 3 * (i - b0)) for i in group}
+        entries, row = [], 0
+        for i in group:
+            entries.append({"id": f"r{i}", "tokens": prompts[i][:pre[i]], "want": list(range(pre[i]))})
+            for t in range(pre[i]):
+                where[(i, t)] = (n, row + t)
+            row += pre[i]
+        steps.append({"step": n, "entries": entries, "end": [f"r{i}" for i in group if pre[i] == len(prompts[i])]})
+        n += 1
+        pos = dict(pre)
+        live = [i for i in group if pos[i] < len(prompts[i])]
+        while live:
+            entries = []
+            for row, i in enumerate(live):
+                entries.append({"id": f"r{i}", "tokens": [prompts[i][pos[i]]], "want": [0]})
+                where[(i, pos[i])] = (n, row)
+                pos[i] += 1
+            ended = [i for i in live if pos[i] == len(prompts[i])]
+            steps.append({"step": n, "entries": entries, "end": [f"r{i}" for i in ended]})
+            live = [i for i in live if i not in ended]
+            n += 1
+    out["batches"] = (steps, where)
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_replay_three_ways(name, dtype):
+    folder = model_folder(name, store_dtype(dtype))
+    lens = [5, 11, 17, 40, 64, 1, 70] if name == "A" else [1, 7, 32, 64, 100, 33, 90]
+    prompts = random_prompts(CONFIGS[name]["vocab_size"], lens, seed=12)
+    refs = [plain_logits(folder, p) for p in prompts]
+    max_tokens = 3 * 128                      # three live requests of at most two pages
+    results = {}
+    for kind, (steps, where) in schedules(prompts).items():
+        out = run_trace(folder, dtype, steps, max_tokens)
+        got = [torch.stack([out[where[(i, t)][0]][where[(i, t)][1]] for t in range(len(p))])
+               for i, p in enumerate(prompts)]
+        results[kind] = got
+        for i, (g, r) in enumerate(zip(got, refs)):
+            for t in range(len(prompts[i])):
+                e = rel_err(g[t:t + 1], r[t:t + 1])
+                assert e < tol(dtype), f"{kind}: request {i} (len {lens[i]}) first wrong position {t}: {e:.3e}"
+    # the three cuttings agree with each other more closely than with the plain implementation
+    close = 5e-6 if dtype == "float32" else tol(dtype)
+    for i in range(len(prompts)):
+        assert rel_err(results["last32"][i], results["whole"][i]) < close
+        assert rel_err(results["batches"][i], results["whole"][i]) < close
+
+
+def test_steps_without_wanted_places_write_no_file_and_empty_home_works(tmp_path):
+    folder = model_folder("A", torch.float32)
+    p = random_prompts(256, [20], seed=1)[0]
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": p[:19], "want": []}], "end": []},
+             {"step": 1, "entries": [{"id": "x", "tokens": p[19:], "want": [0]}], "end": ["x"]},
+             {"step": 2, "entries": [{"id": "x", "tokens": p, "want": [19]}], "end": ["x"]}]
+    env = dict(os.environ, HOME=str(tmp_path / "home"))
+    os.makedirs(env["HOME"])
+    out = run_trace(folder, "float32", steps, 64, env=env)
+    ref = plain_logits(folder, p)[19:20]
+    assert sorted(out) == [1, 2]
+    assert rel_err(out[1], ref) < 1e-4 and rel_err(out[2], ref) < 1e-4

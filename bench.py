@@ -1,0 +1,272 @@
+"""Benchmark: decode and prefill throughput of the Qwen3-4B shape on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B]
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second at the default batch (8), timed on
+the device over K single-token steps after W warm-up steps; ``e2e`` is the same through
+``Model.generate_batch`` with host token ids in and out; ``prefill`` is a 2,048-token prompt;
+``points`` holds decode at batch 1 and 64; ``roofline`` relates the decode step to the memory
+bandwidth.  The model has the layer sizes of the benchmark configuration with random weights and
+synthetic token ids; ``--layers`` runs fewer layers of the same sizes (``config`` names both).
+
+The work is one GPU's: for ``--gpus`` above 1 it says so and exits with 2.  The reference arm
+(``--impl reference``) is unavailable: the reference is a Rust workspace, there is no Rust
+toolchain or network here to build it, and its CUDA path runs none of its kernels for bfloat16
+weights.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# layer sizes of the benchmark configuration (Qwen3-4B shape)
+CONFIG_4B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=36, hidden_size=2560,
+                 num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=9728,
+                 vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True,
+                 max_position_embeddings=40960)
+FULL_LAYERS = 36
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    out = dict(FALLBACK_PEAKS)
+    src = "fallback"
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                data = json.load(f)
+            for k in out:
+                if isinstance(data.get(k), (int, float)) and data[k] > 0:
+                    out[k] = float(data[k])
+            src = "measured"
+        except (OSError, ValueError):
+            pass
+    out["source"] = src
+    return out
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed regions run."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons = [], 0, set()
+        for p in self.samples:
+            try:
+                sm.append(int(float(p[0])))
+                mx = max(mx, int(float(p[1])))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": int(statistics.median(sm)) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def decode_run(model, batch, steps, warmup, seed):
+    """One varlen prefill (untimed), then warm-up and timed single-token steps; device-timed."""
+    import torch
+    from builderforce_inference_b200.engine.engine import SequenceStep
+    eng = model.engine
+    g = torch.Generator().manual_seed(seed)
+    vocab = eng.spec.vocab_size
+    lens = torch.randint(128, 2049, (batch,), generator=g).tolist()
+    prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lens]
+    slots = [eng.acquire() for _ in range(batch)]
+    eng.step([SequenceStep(s, p, ()) for s, p in zip(slots, prompts)], check=False)
+    toks = [int(t) for t in torch.randint(0, vocab, (batch,), generator=g).tolist()]
+
+    def one():
+        return eng.step([SequenceStep(s, (t,), (0,)) for s, t in zip(slots, toks)], check=False)
+
+    for _ in range(warmup):
+        one()
+    torch.cuda.synchronize()
+    bytes_before = eng.decode_step_bytes()
+    launches0 = eng.kernel_launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        one()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    launches = eng.kernel_launches() - launches0
+    step_bytes = (bytes_before + eng.decode_step_bytes()) / 2.0
+    eng.check_status()
+    ctx_mean = sum(eng.length(s) for s in slots) / batch
+    for s in slots:
+        eng.release(s)
+    return {"tok_s": batch * steps / (ms / 1e3), "ms_per_step": ms / steps, "launches": launches,
+            "step_bytes": step_bytes, "ctx_mean": ctx_mean}
+
+
+def e2e_run(model, batch, steps, warmup, seed):
+    """The same through ``Model.generate_batch``: host ids in, host ids out, every step."""
+    import torch
+    from builderforce_inference_b200 import SampleParams
+    g = torch.Generator().manual_seed(seed)
+    vocab = model.n_vocab()
+    lens = torch.randint(128, 2049, (batch,), generator=g).tolist()
+    prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lens]
+    stamps = []
+    model.stepper.on_tokens = lambda n: stamps.append((time.perf_counter(), n))
+    try:
+        model.generate_batch(prompts, SampleParams(max_tokens=warmup + steps + 1), ignore_eos=True)
+    finally:
+        model.stepper.on_tokens = None
+    # stamps[0] follows the prefill; stamps[i] follows decode step i
+    t0, t1 = stamps[warmup][0], stamps[warmup + steps][0]
+    tokens = sum(n for _, n in stamps[warmup + 1:warmup + steps + 1])
+    return {"tok_s": tokens / (t1 - t0), "h2d": model.stepper.h2d_bytes, "d2h": model.stepper.d2h_bytes}
+
+
+def prefill_run(model, tokens, reps, layers):
+    import torch
+    from builderforce_inference_b200.engine.engine import SequenceStep
+    eng = model.engine
+    g = torch.Generator().manual_seed(99)
+    prompt = torch.randint(0, eng.spec.vocab_size, (tokens,), generator=g).tolist()
+    times = []
+    for i in range(reps + 2):
+        s = eng.acquire()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        eng.step([SequenceStep(s, prompt, (tokens - 1,))], check=False)
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= 2:
+            times.append(e0.elapsed_time(e1))
+        eng.release(s)
+    ms = statistics.median(times)
+    c = CONFIG_4B
+    h, d, nq, nkv, inter = c["hidden_size"], c["head_dim"], c["num_attention_heads"], c["num_key_value_heads"], \
+        c["intermediate_size"]
+    per_layer = 2 * tokens * (h * (nq + 2 * nkv) * d + nq * d * h + 3 * h * inter)
+    attn = 4 * nq * d * tokens * (tokens + 1) / 2
+    flops = layers * (per_layer + attn) + 2 * h * c["vocab_size"]
+    return {"ms": ms, "tok_s": tokens / (ms / 1e3), "flops": flops}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="run fewer layers of the same sizes")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Rust workspace: no Rust toolchain or network here to build it, "
+                          "pip cannot install it, and its CUDA backend runs no kernel for bf16 weights"}))
+        return 0
+    if a.gpus != 1:
+        print(f"bench.py measures one GPU: this library has no multi-GPU path (asked for --gpus {a.gpus})")
+        return 2
+    warmup = max(3, a.warmup)
+
+    import torch
+    from builderforce_inference_b200 import Model
+    pk = peaks()
+    cfg = dict(CONFIG_4B, num_hidden_layers=a.layers)
+    max_batch = a.batch if a.no_points else max(64, a.batch)
+    t_load = time.time()
+    model = Model.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=max_batch * CONTEXT, max_seq_len=CONTEXT,
+                              max_batch=max_batch)
+    print(f"[bench] model ready in {time.time() - t_load:.1f} s", file=sys.stderr, flush=True)
+
+    # untimed: compile, capture graphs, size workspaces
+    decode_run(model, a.batch, 2, 3, seed=1)
+    clocks = ClockSampler()
+    clocks.start()
+    main_run = decode_run(model, a.batch, a.steps, warmup, seed=2)
+    e2e = e2e_run(model, a.batch, a.steps, warmup, seed=2)
+    points, prefill = {}, None
+    if not a.no_points:
+        for b in (1, 64):
+            if b == a.batch:
+                points[f"decode_b{b}"] = round(main_run["tok_s"], 1)
+                continue
+            decode_run(model, b, 2, 3, seed=3)
+            points[f"decode_b{b}"] = round(decode_run(model, b, min(a.steps, 32), warmup, seed=4)["tok_s"], 1)
+        pf = prefill_run(model, PREFILL_TOKENS, 5, a.layers)
+        prefill = {"value": round(pf["tok_s"], 1), "tokens": PREFILL_TOKENS, "ms": round(pf["ms"], 3),
+                   "frac": round(pf["flops"] / (pf["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+    clk = clocks.stop()
+
+    achieved = main_run["step_bytes"] / (main_run["ms_per_step"] / 1e3) / 1e9
+    c = CONFIG_4B
+    line = {
+        "metric": "Qwen3-4B bf16 decode tok/s at batch 8 (batch 1/64 in points; prefill tok/s at 2,048 tokens)",
+        "value": round(main_run["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": warmup,
+        "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random weights",
+        "config": {"model": "qwen3-4b-shape", "layers": a.layers, "layers_full": FULL_LAYERS,
+                   "hidden": c["hidden_size"], "q_heads": c["num_attention_heads"],
+                   "kv_heads": c["num_key_value_heads"], "head_dim": c["head_dim"],
+                   "intermediate": c["intermediate_size"], "vocab": c["vocab_size"], "tied_head": True,
+                   "global_batch": a.batch, "seq_len": CONTEXT, "prompt_len": "uniform[128,2048]",
+                   "ctx_mean": round(main_run["ctx_mean"], 1), "parallelism": "single-gpu",
+                   "l2": "weights read per step exceed L2", "peaks": pk["source"]},
+        "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tokens/s", "h2d_bytes_per_step": e2e["h2d"],
+                "d2h_bytes_per_step": e2e["d2h"]},
+        "gpu_launches": main_run["launches"],
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "clocks": clk,
+    }
+    if prefill is not None:
+        line["prefill"] = prefill
+        line["points"] = points
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,362 @@
+// Decode attention for bfloat16: one new token per sequence attends over its cached keys and
+// values (crates/bfi-core/src/cpu.rs:328-392 with T = 1).  The step is bound by reading the cache
+// once, so the work is split over (sequence, kv head, range of pages): each block streams its
+// pages of 64 keys through a two-stage cp.async ring in shared memory, all query heads of the
+// group share the loaded keys and values (they are the 16 rows of the tensor-core tiles), and
+// partial results (running maximum, sum and unnormalised output, float32) go to a scratch buffer
+// that a second kernel merges in a fixed order.
+//
+// Scores, the running maximum and sum, and the output accumulator are float32; exp is
+// ex2.approx on scores pre-multiplied by log2(e).
+#include "common.cuh"
+
+#define AD_WARPS 4
+#define AD_THREADS (AD_WARPS * 32)
+#define AD_TILE 64          // keys per tile = tokens per page
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem_row);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem_row);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// A tile in shared memory: [64 rows][D] bfloat16; the 16-byte chunk c of row r sits at chunk
+// c ^ (r & 7), which makes the 8 row addresses of every ldmatrix fall into distinct banks.
+template <int D>
+__device__ __forceinline__ const bf16* tile_chunk(const bf16* tile, int row, int chunk) {
+    return tile + row * D + ((chunk ^ (row & 7)) << 3);
+}
+
+template <int D>
+__device__ __forceinline__ void load_tile(bf16* dst, const bf16* src) {
+    constexpr int CHUNKS = D / 8;                 // per row
+    for (int i = threadIdx.x; i < AD_TILE * CHUNKS; i += AD_THREADS) {
+        const int row = i / CHUNKS, c = i - row * CHUNKS;
+        cp_async16(dst + row * D + ((c ^ (row & 7)) << 3), src + row * D + c * 8);
+    }
+}
+
+// part_o  [seqs, n_q, splits, D]  float32 unnormalised outputs
+// part_ml [seqs, n_q, splits, 2]  float32 (running max in log2 units, running sum)
+template <int D>
+__global__ void __launch_bounds__(AD_THREADS)
+attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out, long out_stride,
+                        const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+                        const int* __restrict__ block_table, int table_stride, const int* __restrict__ seq_slot,
+                        const int* __restrict__ seq_start, int n_q, int n_kv, int window, float scale_log2,
+                        int head_chunks, float* __restrict__ part_o, float* __restrict__ part_ml) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* ks[2] = {reinterpret_cast<bf16*>(smem_raw), reinterpret_cast<bf16*>(smem_raw) + 2 * AD_TILE * D};
+    bf16* vs[2] = {ks[0] + AD_TILE * D, ks[1] + AD_TILE * D};
+
+    const int seq = blockIdx.z;
+    const int slot = seq_slot[seq];
+    if (slot < 0) return;
+    const int n_splits = gridDim.x, split = blockIdx.x;
+    const int group = n_q / n_kv;
+    const int kvh = blockIdx.y / head_chunks;
+    const int hc = blockIdx.y - kvh * head_chunks;
+    const int head0 = kvh * group + hc * 16;              // first query head of this block
+    const int n_heads = min(16, group - hc * 16);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+
+    const int pos = seq_start[seq];                       // the new token's position; keys lo..pos
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int first_page = lo / AD_TILE, last_page = pos / AD_TILE;
+    const int n_pages = last_page - first_page + 1;
+    const int per_split = (n_pages + n_splits - 1) / n_splits;
+    const int p_beg = first_page + split * per_split;
+    const int p_end = min(last_page + 1, p_beg + per_split);
+
+    // query fragments: rows g and g+8 are heads head0+g, head0+g+8
+    const bf16* qbase = q + (size_t)seq * q_stride;       // one token per sequence: row index = seq
+    uint32_t qa[D / 16][4];
+    {
+        const bool ok_lo = g < n_heads, ok_hi = g + 8 < n_heads;
+        const bf16* q_lo = qbase + (size_t)(head0 + g) * D;
+        const bf16* q_hi = qbase + (size_t)(head0 + g + 8) * D;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+            const int c = kk * 16 + 2 * t;
+            qa[kk][0] = ok_lo ? *reinterpret_cast<const uint32_t*>(q_lo + c) : 0u;
+            qa[kk][1] = ok_hi ? *reinterpret_cast<const uint32_t*>(q_hi + c) : 0u;
+            qa[kk][2] = ok_lo ? *reinterpret_cast<const uint32_t*>(q_lo + c + 8) : 0u;
+            qa[kk][3] = ok_hi ? *reinterpret_cast<const uint32_t*>(q_hi + c + 8) : 0u;
+        }
+    }
+
+    float m_run[2] = {-INFINITY, -INFINITY};
+    float l_run[2] = {0.0f, 0.0f};
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[i][j] = 0.0f;
+
+    const size_t page_elems = (size_t)n_kv * AD_TILE * D;
+    const int* table = block_table + (size_t)slot * table_stride;
+
+    auto issue = [&](int page_idx, int stage) {
+        const int page = table[page_idx];
+        if (page >= 0) {
+            const size_t base = (size_t)page * page_elems + (size_t)kvh * AD_TILE * D;
+            load_tile<D>(ks[stage], k_pages + base);
+            load_tile<D>(vs[stage], v_pages + base);
+        }
+        cp_async_commit();
+    };
+
+    if (p_beg < p_end) issue(p_beg, 0);
+    for (int p = p_beg; p < p_end; ++p) {
+        const int stage = (p - p_beg) & 1;
+        if (p + 1 < p_end) {
+            issue(p + 1, stage ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const bool have_page = table[p] >= 0;
+        const bf16* kt = ks[stage];
+        const bf16* vt = vs[stage];
+        if ((p + 1) * AD_TILE - 1 > pos) {
+            // the page that holds `pos`: its later rows were never written.  Their scores are masked,
+            // but a weight of zero times a stray NaN would still poison the output, so clear them.
+            const int first_bad = pos - p * AD_TILE + 1;
+            constexpr int CHUNKS = D / 8;
+            for (int i = threadIdx.x; i < (AD_TILE - first_bad) * CHUNKS; i += AD_THREADS) {
+                const int row = first_bad + i / CHUNKS, c = i % CHUNKS;
+                *reinterpret_cast<uint4*>(vs[stage] + row * D + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            __syncthreads();
+        }
+
+        // ---- scores of this warp's 16 keys: two n-tiles of 8 keys
+        float s[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s[j][i] = 0.0f;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; kk += 2) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                // four 8x8 matrices: key rows of n-tile j, chunks 2kk .. 2kk+3 (two k16 steps)
+                uint32_t b[4];
+                const int row = warp * 16 + j * 8 + (lane & 7);
+                ldmatrix_x4(b, tile_chunk<D>(kt, row, 2 * kk + (lane >> 3)));
+                mma16816(s[j], qa[kk], b[0], b[1]);
+                mma16816(s[j], qa[kk + 1], b[2], b[3]);
+            }
+        }
+        // ---- mask and online softmax; c0,c1 -> row g, keys 2t,2t+1; c2,c3 -> row g+8
+        const int key0 = p * AD_TILE + warp * 16;
+        float p_frag[2][4];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int key = key0 + j * 8 + 2 * t + c;
+                    float v = s[j][r * 2 + c] * scale_log2;
+                    if (!have_page || key > pos || key < lo) v = -INFINITY;
+                    s[j][r * 2 + c] = v;
+                    mx = fmaxf(mx, v);
+                }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run[r], mx);
+            const float corr = (m_run[r] == -INFINITY) ? 0.0f : fast_exp2(m_run[r] - m_new);
+            float sum = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const float v = s[j][r * 2 + c];
+                    const float pv = (v == -INFINITY) ? 0.0f : fast_exp2(v - m_new);
+                    p_frag[j][r * 2 + c] = pv;
+                    sum += pv;
+                }
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            l_run[r] = l_run[r] * corr + sum;
+            m_run[r] = m_new;
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i) {
+                o[i][r * 2] *= corr;
+                o[i][r * 2 + 1] *= corr;
+            }
+        }
+        // ---- P (16 heads x 16 keys) as the A operand, V rows of these 16 keys as B
+        uint32_t pa[4];
+        pa[0] = pack_bf16(p_frag[0][0], p_frag[0][1]);
+        pa[1] = pack_bf16(p_frag[0][2], p_frag[0][3]);
+        pa[2] = pack_bf16(p_frag[1][0], p_frag[1][1]);
+        pa[3] = pack_bf16(p_frag[1][2], p_frag[1][3]);
+        if (have_page) {
+#pragma unroll
+            for (int dd = 0; dd < D / 8; dd += 2) {
+                uint32_t b[4];
+                const int row = warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+                ldmatrix_x4_trans(b, tile_chunk<D>(vt, row, dd + (lane >> 4)));
+                mma16816(o[dd], pa, b[0], b[1]);
+                mma16816(o[dd + 1], pa, b[2], b[3]);
+            }
+        }
+        __syncthreads();      // the stage is free for the load issued in the next iteration
+    }
+
+    // ---- merge the four warps (each saw a quarter of every tile) through shared memory
+    float* mm = reinterpret_cast<float*>(smem_raw);                 // [warps][16][2]
+    float* oo = mm + AD_WARPS * 16 * 2;                             // [warps][16][D]
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = g + r * 8;
+        if (t == 0) {
+            mm[(warp * 16 + row) * 2] = m_run[r];
+            mm[(warp * 16 + row) * 2 + 1] = l_run[r];
+        }
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+            oo[(size_t)(warp * 16 + row) * D + i * 8 + 2 * t] = o[i][r * 2];
+            oo[(size_t)(warp * 16 + row) * D + i * 8 + 2 * t + 1] = o[i][r * 2 + 1];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n_heads * D; idx += AD_THREADS) {
+        const int row = idx / D, e = idx - row * D;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < AD_WARPS; ++w) m = fmaxf(m, mm[(w * 16 + row) * 2]);
+        float l = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < AD_WARPS; ++w) {
+            const float mw = mm[(w * 16 + row) * 2];
+            const float f = (mw == -INFINITY) ? 0.0f : fast_exp2(mw - m);
+            l += mm[(w * 16 + row) * 2 + 1] * f;
+            acc += oo[(size_t)(w * 16 + row) * D + e] * f;
+        }
+        const int head = head0 + row;
+        if (n_splits == 1) {
+            out[(size_t)seq * out_stride + (size_t)head * D + e] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+        } else {
+            const size_t pi = ((size_t)seq * n_q + head) * n_splits + split;
+            part_o[pi * D + e] = acc;
+            if (e == 0) {
+                part_ml[pi * 2] = m;
+                part_ml[pi * 2 + 1] = l;
+            }
+        }
+    }
+}
+
+// Merges the splits of every (sequence, head) in split order.
+template <int D>
+__global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                              const int* __restrict__ seq_slot, bf16* __restrict__ out,
+                                              long out_stride, int n_q, int n_splits) {
+    const int seq = blockIdx.y, head = blockIdx.x;
+    if (seq_slot[seq] < 0) return;
+    const size_t base = ((size_t)seq * n_q + head) * n_splits;
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
+    for (int e = threadIdx.x; e < D; e += blockDim.x) {
+        float l = 0.0f, acc = 0.0f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = part_ml[(base + s) * 2];
+            const float f = (ms == -INFINITY) ? 0.0f : fast_exp2(ms - m);
+            l += part_ml[(base + s) * 2 + 1] * f;
+            acc += part_o[(base + s) * D + e] * f;
+        }
+        out[(size_t)seq * out_stride + (size_t)head * D + e] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+    }
+}
+
+template <int D>
+static int launch_decode(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
+                         const void* v_pages, const int* block_table, int table_stride, const int* seq_slot,
+                         const int* seq_start, int n_seqs, int n_q, int n_kv, int window, float scale, int n_splits,
+                         float* part_o, float* part_ml, cudaStream_t stream) {
+    const int group = n_q / n_kv;
+    const int head_chunks = (group + 15) / 16;
+    const size_t smem = (size_t)4 * AD_TILE * D * sizeof(bf16);
+    const size_t merge_smem = (size_t)AD_WARPS * 16 * (2 + D) * sizeof(float);
+    const size_t need = smem > merge_smem ? smem : merge_smem;
+    auto kernel = attention_decode_kernel<D>;
+    if (need > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need);
+        if (e != cudaSuccess) return bfi_fail("attention_decode: cannot reserve %zu bytes of shared memory: %s", need,
+                                              cudaGetErrorString(e));
+    }
+    dim3 grid(n_splits, n_kv * head_chunks, n_seqs);
+    const float scale_log2 = scale * 1.4426950408889634f;
+    kernel<<<grid, AD_THREADS, need, stream>>>((const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages,
+                                               (const bf16*)v_pages, block_table, table_stride, seq_slot, seq_start,
+                                               n_q, n_kv, window, scale_log2, head_chunks, part_o, part_ml);
+    int rc = bfi_check_launch("attention_decode");
+    if (rc || n_splits == 1) return rc;
+    dim3 mgrid(n_q, n_seqs);
+    attention_decode_merge_kernel<D><<<mgrid, D <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, seq_slot, (bf16*)out,
+                                                                             out_stride, n_q, n_splits);
+    return bfi_check_launch("attention_decode_merge");
+}
+
+// Floats of scratch the call needs for its partial results: [0] outputs, [1] max/sum pairs.
+extern "C" int bfi_attention_decode_scratch(int n_seqs, int n_q, int head_dim, int n_splits, long* sizes) {
+    sizes[0] = n_splits > 1 ? (long)n_seqs * n_q * n_splits * head_dim : 0;
+    sizes[1] = n_splits > 1 ? (long)n_seqs * n_q * n_splits * 2 : 0;
+    return 0;
+}
+
+// Returns 0 on success, 1 on error, 2 when the shape is not taken (nothing launched).
+extern "C" int bfi_attention_decode_bf16(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
+                                         const void* v_pages, const int* block_table, int table_stride,
+                                         const int* seq_slot, const int* seq_start, int n_seqs, int n_q, int n_kv,
+                                         int d, int window, float scale, int n_splits, float* part_o, float* part_ml,
+                                         cudaStream_t stream) {
+    BFI_REQUIRE(n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_decode: %d query heads do not divide into %d kv heads",
+                n_q, n_kv);
+    BFI_REQUIRE(window >= 0 && n_splits >= 1 && n_splits <= 65535, "attention_decode: bad window or split count");
+    if (n_seqs <= 0) return 0;
+    if (d != 64 && d != 128) return 2;
+    if (q_stride % 8 != 0 || ((uintptr_t)q & 15) || n_seqs > 65535) return 2;
+    if (n_splits > 1) BFI_REQUIRE(part_o && part_ml, "attention_decode: split runs need the scratch buffers");
+    if (d == 64)
+        return launch_decode<64>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride, seq_slot,
+                                 seq_start, n_seqs, n_q, n_kv, window, scale, n_splits, part_o, part_ml, stream);
+    return launch_decode<128>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride, seq_slot,
+                              seq_start, n_seqs, n_q, n_kv, window, scale, n_splits, part_o, part_ml, stream);
+}

@@ -3,8 +3,55 @@ take the shape (the caller then uses the general kernel); it never computes a wr
 """
 from __future__ import annotations
 
+from ctypes import c_float, c_int, c_long, c_void_p
+
 import torch
+
+from .library import KernelError, library
+from .ops import _ptr, _rows_2d, _stream, dtype_code
+
+SKINNY_MAX_ROWS = 64
+SM_COUNT = 148
 
 
 def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int) -> bool:
-    return False
+    """bfloat16 x bfloat16 -> ``out`` (float32 or bfloat16).  Few rows: the weight streamer."""
+    m, k = a.shape
+    n = w.shape[0]
+    if m > SKINNY_MAX_ROWS:
+        return False
+    _rows_2d(a, "A")
+    _rows_2d(w, "W")
+    _rows_2d(out, "C")
+    cols = n // 2 if epilogue == 2 else n
+    if w.shape[1] != k or out.shape != (m, cols):
+        raise KernelError(f"matrix product: A {tuple(a.shape)}, W {tuple(w.shape)}, output {tuple(out.shape)}")
+    return library("fast").call_optional(
+        "bfi_skinny_gemm_bf16", _ptr(a), c_long(a.stride(0)), _ptr(w), c_long(w.stride(0)), _ptr(out),
+        c_int(dtype_code(out.dtype)), c_long(out.stride(0)), c_int(m), c_int(n), c_int(k), c_int(epilogue), _stream())
+
+
+def decode_splits(n_seqs: int, n_kv: int, group: int, max_pages: int) -> int:
+    """How many page ranges each (sequence, kv head) is cut into: enough blocks to fill the GPU a
+    few times over, never more than a sequence can have pages.  Depends only on sizes that are
+    fixed when a step is captured."""
+    blocks = n_seqs * n_kv * ((group + 15) // 16)
+    want = (SM_COUNT * 4 + blocks - 1) // blocks
+    return max(1, min(want, max_pages, 64))
+
+
+def attention_decode_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float) -> bool:
+    d = kv.head_dim
+    if d not in (64, 128) or qkv.dtype != torch.bfloat16 or kv.k.dtype != torch.bfloat16:
+        return False
+    max_pages = kv.block_table.shape[1]
+    splits = decode_splits(ctx.n_seqs, kv.n_kv_heads, n_heads // kv.n_kv_heads, max_pages)
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = ctx.workspace.vector("attn.part_o", ctx.n_seqs * n_heads * splits * d, torch.float32)
+        part_ml = ctx.workspace.vector("attn.part_ml", ctx.n_seqs * n_heads * splits * 2, torch.float32)
+    return library("fast").call_optional(
+        "bfi_attention_decode_bf16", _ptr(qkv), c_long(qkv.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(kv.k),
+        _ptr(kv.v), _ptr(kv.block_table), c_int(kv.block_table.stride(0)), _ptr(ctx.seq_slot), _ptr(ctx.seq_start),
+        c_int(ctx.n_seqs), c_int(n_heads), c_int(kv.n_kv_heads), c_int(d), c_int(kv.window or 0), c_float(scale),
+        c_int(splits), _ptr(part_o), _ptr(part_ml), _stream())

@@ -35,6 +35,28 @@ class KernelLibrary:
         self._funcs: Dict[str, ctypes._CFuncPtr] = {}
         self.calls = 0          # exported functions called so far (each launches at least one kernel)
 
+    def call_optional(self, func: str, *args) -> bool:
+        """For kernels that may decline a shape: True if it ran, False if it declined (code 2)."""
+        f = self._function(func)
+        rc = f(*args)
+        if rc == 2:
+            return False
+        self.calls += 1
+        if rc != 0:
+            raise KernelError(self.lib.bfi_last_error().decode("utf-8", "replace"))
+        return True
+
+    def _function(self, func: str):
+        f = self._funcs.get(func)
+        if f is None:
+            try:
+                f = getattr(self.lib, func)
+            except AttributeError as e:
+                raise KernelError(f"kernel library '{self.name}' has no function {func}") from e
+            f.restype = ctypes.c_int
+            self._funcs[func] = f
+        return f
+
     def call(self, func: str, *args) -> None:
         f = self._funcs.get(func)
         if f is None:

@@ -39,7 +39,16 @@ TINY_D = _cfg(num_hidden_layers=2, hidden_size=80, num_attention_heads=5, num_ke
               intermediate_size=144, vocab_size=259, rope_theta=10000.0, rms_norm_eps=1e-6,
               tie_word_embeddings=True, max_position_embeddings=1024)
 
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+# head sizes the bfloat16 decode attention takes (64 and 128), groups of 4 and 2, a window of 70
+TINY_E = _cfg(num_hidden_layers=2, hidden_size=128, num_attention_heads=8, num_key_value_heads=2, head_dim=64,
+              intermediate_size=192, vocab_size=500, rope_theta=10000.0, rms_norm_eps=1e-6,
+              tie_word_embeddings=True, max_position_embeddings=512, use_sliding_window=True,
+              sliding_window=70, max_window_layers=1)
+TINY_F = _cfg(num_hidden_layers=2, hidden_size=96, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+              intermediate_size=160, vocab_size=333, rope_theta=1000000.0, rms_norm_eps=1e-6,
+              tie_word_embeddings=False, max_position_embeddings=1024)
+
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F}
 
 F32_TOL = 1e-4     # max |got - ref| / max |ref|, float32 run against the plain implementation
 BF16_TOL = 2e-2    # bfloat16 run against the plain implementation on the same (bfloat16) weights

@@ -37,7 +37,7 @@ def first_bad_row(got, ref, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_each_request_alone_and_whole(name, dtype):
     eng = load(name, dtype)
     folder = model_folder(name, store_dtype(dtype))
@@ -55,7 +55,7 @@ def test_each_request_alone_and_whole(name, dtype):
 
 @pytest.mark.parametrize("graphs", [False, True])
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "E", "F"])
 def test_last_32_tokens_one_by_one(name, dtype, graphs):
     eng = load(name, dtype, use_graphs=graphs)
     folder = model_folder(name, store_dtype(dtype))
@@ -74,7 +74,7 @@ def test_last_32_tokens_one_by_one(name, dtype, graphs):
 
 @pytest.mark.parametrize("graphs", [False, True])
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "E", "F"])
 def test_unequal_batches_one_after_another(name, dtype, graphs):
     """Batches start together (one step with every prompt prefix), then one token each; shorter
     requests end earlier and give their slot back; the next batch reuses slots and pages that
@@ -120,9 +120,9 @@ def test_unequal_batches_one_after_another(name, dtype, graphs):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_long_decoding(dtype):
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_long_decoding(name, dtype):
     """Hundreds of single-token steps across many page edges, two sequences of different phase."""
-    name = "D"
     eng = load(name, dtype)
     folder = model_folder(name, store_dtype(dtype))
     pa, pb = random_prompts(CONFIGS[name]["vocab_size"], [400, 333], seed=31)

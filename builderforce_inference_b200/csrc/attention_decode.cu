@@ -74,6 +74,8 @@ attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
                         const int* __restrict__ block_table, int table_stride, const int* __restrict__ seq_slot,
                         const int* __restrict__ seq_start, int n_q, int n_kv, int window, float scale_log2,
                         int head_chunks, float* __restrict__ part_o, float* __restrict__ part_ml) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* ks[2] = {reinterpret_cast<bf16*>(smem_raw), reinterpret_cast<bf16*>(smem_raw) + 2 * AD_TILE * D};
     bf16* vs[2] = {ks[0] + AD_TILE * D, ks[1] + AD_TILE * D};
@@ -288,6 +290,8 @@ template <int D>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               const int* __restrict__ seq_slot, bf16* __restrict__ out,
                                               long out_stride, int n_q, int n_splits) {
+    pdl_trigger();
+    pdl_wait();
     const int seq = blockIdx.y, head = blockIdx.x;
     if (seq_slot[seq] < 0) return;
     const size_t base = ((size_t)seq * n_q + head) * n_splits;
@@ -323,13 +327,13 @@ static int launch_decode(const void* q, long q_stride, void* out, long out_strid
     }
     dim3 grid(n_splits, n_kv * head_chunks, n_seqs);
     const float scale_log2 = scale * 1.4426950408889634f;
-    kernel<<<grid, AD_THREADS, need, stream>>>((const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages,
+    bfi_launch(kernel, dim3(grid), dim3(AD_THREADS), need, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages,
                                                (const bf16*)v_pages, block_table, table_stride, seq_slot, seq_start,
                                                n_q, n_kv, window, scale_log2, head_chunks, part_o, part_ml);
     int rc = bfi_check_launch("attention_decode");
     if (rc || n_splits == 1) return rc;
     dim3 mgrid(n_q, n_seqs);
-    attention_decode_merge_kernel<D><<<mgrid, D <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, seq_slot, (bf16*)out,
+    bfi_launch(attention_decode_merge_kernel<D>, dim3(mgrid), dim3(D <= 64 ? 64 : 128), 0, stream, part_o, part_ml, seq_slot, (bf16*)out,
                                                                              out_stride, n_q, n_splits);
     return bfi_check_launch("attention_decode_merge");
 }

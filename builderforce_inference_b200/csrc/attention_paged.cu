@@ -26,6 +26,8 @@ attention_paged_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
                        const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_seqlens,
                        const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int n_q, int n_kv, int d,
                        int gh, int head_chunks, int window, float scale) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float smem[];
     float* qs = smem;                          // [ATT_ROWS][d]
     float* ks = qs + ATT_ROWS * d;             // [ATT_KEYS][d + 1]
@@ -173,7 +175,7 @@ static int launch_attention(const void* q, long q_stride, void* out, long out_st
         if (e != cudaSuccess) return bfi_fail("attention_paged: cannot reserve %zu bytes of shared memory: %s", smem,
                                               cudaGetErrorString(e));
     }
-    kernel<<<grid, ATT_WARPS * 32, smem, stream>>>((const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages,
+    bfi_launch(kernel, dim3(grid), dim3(ATT_WARPS * 32), smem, stream, (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages,
                                                    (const T*)v_pages, block_table, table_stride, cu_seqlens, seq_slot,
                                                    seq_start, n_q, n_kv, d, gh, head_chunks, window, scale);
     return bfi_check_launch("attention_paged");

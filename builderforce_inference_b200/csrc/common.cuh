@@ -29,6 +29,31 @@ extern "C" const char* bfi_last_error();
 int bfi_fail(const char* fmt, ...);
 int bfi_check_launch(const char* what);
 
+// Programmatic dependent launch.  When enabled, every kernel is launched with the attribute that
+// lets it start while its predecessor in the stream drains.  A kernel may touch nothing but
+// constant weights before pdl_wait(), which returns once the predecessor has completed and its
+// writes are visible; without the attribute the instruction returns at once.
+extern int g_bfi_pdl;
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t bfi_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_bfi_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 #define BFI_REQUIRE(cond, ...)                  \
     do {                                        \
         if (!(cond)) return bfi_fail(__VA_ARGS__); \

@@ -16,6 +16,8 @@
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                   float* __restrict__ out, int width, int vocab, int* status) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * width;
@@ -36,9 +38,9 @@ extern "C" int bfi_embed_rows(const void* table, int table_dtype, const int* ids
     if (n_tokens == 0) return 0;
     const int threads = width >= 1024 ? 256 : 128;
     if (table_dtype == BFI_F32)
-        embed_rows_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, out, width, vocab, status);
+        bfi_launch(embed_rows_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)table, ids, out, width, vocab, status);
     else
-        embed_rows_kernel<bf16><<<n_tokens, threads, 0, stream>>>((const bf16*)table, ids, out, width, vocab, status);
+        bfi_launch(embed_rows_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, (const bf16*)table, ids, out, width, vocab, status);
     return bfi_check_launch("embed_rows");
 }
 
@@ -50,6 +52,8 @@ template <typename TX>
 __global__ void rmsnorm_kernel(const TX* __restrict__ x, long x_stride, const int* __restrict__ rows,
                                const void* __restrict__ w, int w_dtype, void* __restrict__ out,
                                int out_dtype, long out_stride, int width, float eps) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const long src = rows ? (long)rows[r] : (long)r;
@@ -68,6 +72,55 @@ __global__ void rmsnorm_kernel(const TX* __restrict__ x, long x_stride, const in
     }
 }
 
+// Single pass for float32 rows whose width is a multiple of 4 and at most 4 * VPT * 256: the row
+// stays in registers between the sum of squares and the scaling, so it is read once.
+template <int VPT>
+__global__ void __launch_bounds__(256)
+rmsnorm_regs_kernel(const float* __restrict__ x, long x_stride, const int* __restrict__ rows,
+                    const void* __restrict__ w, int w_dtype, void* __restrict__ out, int out_dtype,
+                    long out_stride, int width, float eps) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const long src = rows ? (long)rows[r] : (long)r;
+    const float4* xr = reinterpret_cast<const float4*>(x + src * x_stride);
+    const int n4 = width >> 2;
+    float4 v[VPT];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int j = i * 256 + threadIdx.x;
+        v[i] = j < n4 ? xr[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss = fmaf(v[i].x, v[i].x, ss);
+        ss = fmaf(v[i].y, v[i].y, ss);
+        ss = fmaf(v[i].z, v[i].z, ss);
+        ss = fmaf(v[i].w, v[i].w, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    const size_t obase = (size_t)r * out_stride;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int j = i * 256 + threadIdx.x;
+        if (j >= n4) continue;
+        const int c = j * 4;
+        const float o0 = v[i].x * scale * load_as_f32(w, w_dtype, c);
+        const float o1 = v[i].y * scale * load_as_f32(w, w_dtype, c + 1);
+        const float o2 = v[i].z * scale * load_as_f32(w, w_dtype, c + 2);
+        const float o3 = v[i].w * scale * load_as_f32(w, w_dtype, c + 3);
+        if (out_dtype == BFI_F32) {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + obase + c) = make_float4(o0, o1, o2, o3);
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(o0, o1), hi = __floats2bfloat162_rn(o2, o3);
+            uint2 packed;
+            packed.x = *reinterpret_cast<uint32_t*>(&lo);
+            packed.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(out) + obase + c) = packed;
+        }
+    }
+}
+
 extern "C" int bfi_rmsnorm(const void* x, int x_dtype, long x_stride, const int* rows, const void* w,
                            int w_dtype, void* out, int out_dtype, long out_stride, int n_rows, int width,
                            float eps, cudaStream_t stream) {
@@ -75,12 +128,26 @@ extern "C" int bfi_rmsnorm(const void* x, int x_dtype, long x_stride, const int*
     BFI_REQUIRE(n_rows >= 0 && width > 0, "rmsnorm: bad sizes rows=%d width=%d", n_rows, width);
     BFI_REQUIRE(x_stride >= width && out_stride >= width, "rmsnorm: row stride shorter than the row");
     if (n_rows == 0) return 0;
+    const bool vec = x_dtype == BFI_F32 && width % 4 == 0 && x_stride % 4 == 0 && out_stride % 4 == 0 &&
+                     ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0 && width <= 4 * 4 * 256;
+    if (vec) {
+        const int vpt = (width / 4 + 255) / 256;
+#define BFI_NORM(V)                                                                                             \
+    bfi_launch(rmsnorm_regs_kernel<V>, dim3(n_rows), dim3(256), 0, stream, (const float*)x, x_stride, rows, w,  \
+               w_dtype, out, out_dtype, out_stride, width, eps)
+        if (vpt <= 1) BFI_NORM(1);
+        else if (vpt == 2) BFI_NORM(2);
+        else if (vpt == 3) BFI_NORM(3);
+        else BFI_NORM(4);
+#undef BFI_NORM
+        return bfi_check_launch("rmsnorm");
+    }
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
     if (x_dtype == BFI_F32)
-        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>((const float*)x, x_stride, rows, w, w_dtype, out,
+        bfi_launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, (const float*)x, x_stride, rows, w, w_dtype, out,
                                                               out_dtype, out_stride, width, eps);
     else
-        rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>((const bf16*)x, x_stride, rows, w, w_dtype, out,
+        bfi_launch(rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, (const bf16*)x, x_stride, rows, w, w_dtype, out,
                                                              out_dtype, out_stride, width, eps);
     return bfi_check_launch("rmsnorm");
 }
@@ -104,6 +171,8 @@ __device__ __forceinline__ float silu_f32(float g) {
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, long in_stride, T* __restrict__ out, long out_stride,
                                 int n_rows, int inter, int interleaved) {
+    pdl_trigger();
+    pdl_wait();
     const long total = (long)n_rows * inter;
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
         const long r = i / inter;
@@ -125,10 +194,10 @@ extern "C" int bfi_silu_mul(const void* gu, long in_stride, void* out, long out_
     const int threads = 256;
     const int blocks = (int)((total + threads - 1) / threads < 148L * 16 ? (total + threads - 1) / threads : 148L * 16);
     if (dtype == BFI_F32)
-        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, in_stride, (float*)out, out_stride,
+        bfi_launch(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)gu, in_stride, (float*)out, out_stride,
                                                                n_rows, inter, interleaved);
     else
-        silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, in_stride, (bf16*)out, out_stride,
+        bfi_launch(silu_mul_kernel<bf16>, dim3(blocks), dim3(threads), 0, stream, (const bf16*)gu, in_stride, (bf16*)out, out_stride,
                                                               n_rows, inter, interleaved);
     return bfi_check_launch("silu_mul");
 }
@@ -154,6 +223,8 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, long token_stride
                                           const int* __restrict__ token_slot, T* __restrict__ k_pages,
                                           T* __restrict__ v_pages, const int* __restrict__ block_table,
                                           int table_stride, int flags, int* status) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float buf[QKR_WARPS][QKR_MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = n_q + 2 * n_kv;
@@ -252,12 +323,12 @@ extern "C" int bfi_qk_norm_rope_cache(void* qkv, int dtype, long token_stride, i
     const long items = (long)n_tokens * (n_q + 2 * n_kv);
     const int blocks = (int)((items + QKR_WARPS - 1) / QKR_WARPS);
     if (dtype == BFI_F32)
-        qk_norm_rope_cache_kernel<float><<<blocks, QKR_WARPS * 32, 0, stream>>>(
+        bfi_launch(qk_norm_rope_cache_kernel<float>, dim3(blocks), dim3(QKR_WARPS * 32), 0, stream, 
             (float*)qkv, token_stride, n_tokens, n_q, n_kv, d, q_norm_w, k_norm_w, norm_dtype, eps,
             (const float2*)rope_table, rot_dim, table_positions, token_pos, token_slot, (float*)k_pages,
             (float*)v_pages, block_table, table_stride, flags, status);
     else
-        qk_norm_rope_cache_kernel<bf16><<<blocks, QKR_WARPS * 32, 0, stream>>>(
+        bfi_launch(qk_norm_rope_cache_kernel<bf16>, dim3(blocks), dim3(QKR_WARPS * 32), 0, stream, 
             (bf16*)qkv, token_stride, n_tokens, n_q, n_kv, d, q_norm_w, k_norm_w, norm_dtype, eps,
             (const float2*)rope_table, rot_dim, table_positions, token_pos, token_slot, (bf16*)k_pages,
             (bf16*)v_pages, block_table, table_stride, flags, status);
@@ -270,6 +341,8 @@ extern "C" int bfi_qk_norm_rope_cache(void* qkv, int dtype, long token_stride, i
 // out[i] += add[i]  (float32 residual stream += an activation)
 template <typename T>
 __global__ void residual_add_kernel(float* __restrict__ x, const T* __restrict__ y, long n) {
+    pdl_trigger();
+    pdl_wait();
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x)
         x[i] += to_f32(y[i]);
 }
@@ -281,8 +354,8 @@ extern "C" int bfi_residual_add(float* x, const void* y, int y_dtype, long n, cu
     const long want = (n + threads - 1) / threads;
     const int blocks = (int)(want < 148L * 16 ? want : 148L * 16);
     if (y_dtype == BFI_F32)
-        residual_add_kernel<float><<<blocks, threads, 0, stream>>>(x, (const float*)y, n);
+        bfi_launch(residual_add_kernel<float>, dim3(blocks), dim3(threads), 0, stream, x, (const float*)y, n);
     else
-        residual_add_kernel<bf16><<<blocks, threads, 0, stream>>>(x, (const bf16*)y, n);
+        bfi_launch(residual_add_kernel<bf16>, dim3(blocks), dim3(threads), 0, stream, x, (const bf16*)y, n);
     return bfi_check_launch("residual_add");
 }

@@ -22,5 +22,14 @@ int bfi_check_launch(const char* what) {
     return 0;
 }
 
+// Off unless asked for: measured on the decode step, early launch of dependents did not pay.
+int g_bfi_pdl = 0;
+
+// Turns programmatic dependent launch on (1) or off (0) for every later launch of this library.
+extern "C" int bfi_set_pdl(int on) {
+    g_bfi_pdl = on ? 1 : 0;
+    return 0;
+}
+
 // Identifies the build: the architecture the device code was compiled for.
 extern "C" const char* bfi_build_arch() { return "sm_100a"; }

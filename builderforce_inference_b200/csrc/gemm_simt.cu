@@ -38,6 +38,8 @@ template <typename TA, typename TW>
 __global__ void __launch_bounds__(256)
 gemm_tile_kernel(const TA* __restrict__ A, long lda, const TW* __restrict__ W, long ldw, void* __restrict__ C,
                  int c_dtype, long ldc, int M, int N, int K, int epilogue) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ __align__(16) float As[TK][TM + TPAD];
     __shared__ __align__(16) float Ws[TK][TN + TPAD];
     const int tid = threadIdx.x;
@@ -119,6 +121,8 @@ template <typename TA, typename TW, int MB>
 __global__ void __launch_bounds__(256)
 gemv_rows_kernel(const TA* __restrict__ A, long lda, const TW* __restrict__ W, long ldw, void* __restrict__ C,
                  int c_dtype, long ldc, int m_base, int M, int N, int K, int epilogue) {
+    pdl_trigger();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int pair = blockIdx.x * (blockDim.x >> 5) + warp;
     const int n_a = pair * 2, n_b = n_a + 1;
@@ -173,23 +177,23 @@ static int launch_simt(const void* A, long lda, const void* W, long ldw, void* C
         for (int m_base = 0; m_base < M; m_base += 8) {
             const int left = M - m_base;
             if (left >= 5)
-                gemv_rows_kernel<TA, TW, 8><<<blocks, warps * 32, 0, stream>>>((const TA*)A, lda, (const TW*)W, ldw, C,
+                bfi_launch(gemv_rows_kernel<TA, TW, 8>, dim3(blocks), dim3(warps * 32), 0, stream, (const TA*)A, lda, (const TW*)W, ldw, C,
                                                                               c_dtype, ldc, m_base, M, N, K, epilogue);
             else if (left >= 3)
-                gemv_rows_kernel<TA, TW, 4><<<blocks, warps * 32, 0, stream>>>((const TA*)A, lda, (const TW*)W, ldw, C,
+                bfi_launch(gemv_rows_kernel<TA, TW, 4>, dim3(blocks), dim3(warps * 32), 0, stream, (const TA*)A, lda, (const TW*)W, ldw, C,
                                                                               c_dtype, ldc, m_base, M, N, K, epilogue);
             else if (left == 2)
-                gemv_rows_kernel<TA, TW, 2><<<blocks, warps * 32, 0, stream>>>((const TA*)A, lda, (const TW*)W, ldw, C,
+                bfi_launch(gemv_rows_kernel<TA, TW, 2>, dim3(blocks), dim3(warps * 32), 0, stream, (const TA*)A, lda, (const TW*)W, ldw, C,
                                                                               c_dtype, ldc, m_base, M, N, K, epilogue);
             else
-                gemv_rows_kernel<TA, TW, 1><<<blocks, warps * 32, 0, stream>>>((const TA*)A, lda, (const TW*)W, ldw, C,
+                bfi_launch(gemv_rows_kernel<TA, TW, 1>, dim3(blocks), dim3(warps * 32), 0, stream, (const TA*)A, lda, (const TW*)W, ldw, C,
                                                                               c_dtype, ldc, m_base, M, N, K, epilogue);
         }
         return bfi_check_launch("gemv_rows");
     }
     dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM);
     BFI_REQUIRE(grid.y <= 65535, "gemm_simt: M=%d is too large for one launch", M);
-    gemm_tile_kernel<TA, TW><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, ldw, C, c_dtype, ldc, M, N, K,
+    bfi_launch(gemm_tile_kernel<TA, TW>, dim3(grid), dim3(256), 0, stream, (const TA*)A, lda, (const TW*)W, ldw, C, c_dtype, ldc, M, N, K,
                                                       epilogue);
     return bfi_check_launch("gemm_tile");
 }

@@ -72,6 +72,8 @@ sample_rows_kernel(const float* __restrict__ logits, long stride, float* __restr
                    const int* __restrict__ seen, const int* __restrict__ seen_cu, const float* __restrict__ temperature,
                    const float* __restrict__ u_draw, float repeat_penalty, float presence_penalty, float min_p,
                    int* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ ArgBest abest[33];
     __shared__ float fscratch[33];
     __shared__ float warp_tot[32];
@@ -200,7 +202,7 @@ extern "C" int bfi_sample_rows(const float* logits, long stride, float* work, in
         BFI_REQUIRE(work != nullptr && seen != nullptr, "sample_rows: penalties need a work buffer and the seen ids");
     BFI_REQUIRE(repeat_penalty > 0.0f, "sample_rows: repeat_penalty must be positive");
     if (n_rows == 0) return 0;
-    sample_rows_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, stride, work, vocab, seen, seen_cu, temperature,
+    bfi_launch(sample_rows_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, stride, work, vocab, seen, seen_cu, temperature,
                                                              u_draw, repeat_penalty, presence_penalty, min_p, out);
     return bfi_check_launch("sample_rows");
 }
@@ -208,6 +210,8 @@ extern "C" int bfi_sample_rows(const float* logits, long stride, float* work, in
 // Greedy only: out[row] = lowest index of the row maximum.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_rows_kernel(const float* __restrict__ logits, long stride, int vocab, int* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ ArgBest abest[33];
     const float* x = logits + (size_t)blockIdx.x * stride;
     ArgBest mine;
@@ -224,10 +228,72 @@ argmax_rows_kernel(const float* __restrict__ logits, long stride, int vocab, int
     if (threadIdx.x == 0) out[blockIdx.x] = best.i == 0x7fffffff ? 0 : best.i;
 }
 
-extern "C" int bfi_argmax_rows(const float* logits, long stride, int n_rows, int vocab, int* out, cudaStream_t stream) {
+// Large vocabularies: the row is cut into chunks, one block each, and a second kernel picks among
+// the chunks' winners; ties still go to the lowest index.
+#define ARGMAX_CHUNK 8192
+
+__global__ void __launch_bounds__(256)
+argmax_chunks_kernel(const float* __restrict__ logits, long stride, int vocab, int n_chunks, float* __restrict__ best_v,
+                     int* __restrict__ best_i) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ ArgBest abest[33];
+    const int row = blockIdx.y, chunk = blockIdx.x;
+    const float* x = logits + (size_t)row * stride;
+    const int beg = chunk * ARGMAX_CHUNK, end = min(vocab, beg + ARGMAX_CHUNK);
+    ArgBest mine;
+    mine.v = -INFINITY;
+    mine.i = 0x7fffffff;
+    for (int j = beg + threadIdx.x; j < end; j += blockDim.x) {
+        const float v = x[j];
+        if (v > mine.v) {
+            mine.v = v;
+            mine.i = j;
+        }
+    }
+    const ArgBest best = block_argmax(mine, abest);
+    if (threadIdx.x == 0) {
+        best_v[(size_t)row * n_chunks + chunk] = best.v;
+        best_i[(size_t)row * n_chunks + chunk] = best.i;
+    }
+}
+
+__global__ void __launch_bounds__(64)
+argmax_pick_kernel(const float* __restrict__ best_v, const int* __restrict__ best_i, int n_chunks, int* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ ArgBest abest[33];
+    const int row = blockIdx.x;
+    ArgBest mine;
+    mine.v = -INFINITY;
+    mine.i = 0x7fffffff;
+    for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) {
+        ArgBest o;
+        o.v = best_v[(size_t)row * n_chunks + c];
+        o.i = best_i[(size_t)row * n_chunks + c];
+        mine = better(mine, o);
+    }
+    const ArgBest best = block_argmax(mine, abest);
+    if (threadIdx.x == 0) out[row] = best.i == 0x7fffffff ? 0 : best.i;
+}
+
+// `scratch` (optional) holds 2 * n_rows * ceil(vocab / 8192) 4-byte values; with it, large
+// vocabularies are searched by many blocks per row.
+extern "C" int bfi_argmax_rows(const float* logits, long stride, int n_rows, int vocab, int* out, void* scratch,
+                               long scratch_values, cudaStream_t stream) {
     BFI_REQUIRE(n_rows >= 0 && vocab > 0, "argmax_rows: bad sizes rows=%d vocab=%d", n_rows, vocab);
     BFI_REQUIRE(stride >= vocab, "argmax_rows: row stride shorter than the vocabulary");
     if (n_rows == 0) return 0;
-    argmax_rows_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, stride, vocab, out);
+    const int n_chunks = (vocab + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
+    if (scratch != nullptr && n_chunks > 1 && scratch_values >= 2L * n_rows * n_chunks && n_rows <= 65535) {
+        float* bv = reinterpret_cast<float*>(scratch);
+        int* bi = reinterpret_cast<int*>(scratch) + (size_t)n_rows * n_chunks;
+        bfi_launch(argmax_chunks_kernel, dim3(n_chunks, n_rows), dim3(256), 0, stream, logits, stride, vocab, n_chunks, bv, bi);
+        int rc = bfi_check_launch("argmax_chunks");
+        if (rc) return rc;
+        bfi_launch(argmax_pick_kernel, dim3(n_rows), dim3(64), 0, stream, (const float*)bv, (const int*)bi, n_chunks, out);
+        return bfi_check_launch("argmax_pick");
+    }
+    bfi_launch(argmax_rows_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, stride, vocab, out);
     return bfi_check_launch("argmax_rows");
 }

@@ -41,9 +41,10 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     return v;
 }
 
-__device__ __forceinline__ uint4 ldg_cached(const void* p) {
+// Activations are written by the preceding kernel: read through L2 (never a stale L1 line), after the wait.
+__device__ __forceinline__ uint4 ldg_plain(const void* p) {
     uint4 v;
-    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
 
@@ -60,7 +61,8 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
 template <int NT, int RT, int U>
 __global__ void skinny_gemm_kernel(const bf16* __restrict__ A, long lda, const bf16* __restrict__ W, long ldw,
                                    void* __restrict__ C, int c_dtype, long ldc, int M, int N, int K, int k_per_warp,
-                                   int epilogue) {
+                                   int epilogue, int prefetch, int ksplit, float* __restrict__ scratch,
+                                   int* __restrict__ counters) {
     extern __shared__ float red[];   // [warps][RT*16][NT*8 + 1]
     constexpr int R = RT * 16;
     constexpr int MP = NT * 8;
@@ -96,37 +98,69 @@ __global__ void skinny_gemm_kernel(const bf16* __restrict__ A, long lda, const b
         arow[n] = A + (size_t)(arow_ok[n] ? m : 0) * lda;
     }
 
-    const int kbeg = warp * k_per_warp;
+    // grid.y splits K between blocks, the warps of a block split the block's share
+    const int kblock = blockIdx.y * k_per_warp * n_warps;
+    const int kbeg = min(K, kblock + warp * k_per_warp);
     const int kend = min(K, kbeg + k_per_warp);
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
-    for (int k0 = kbeg; k0 < kend; k0 += 32 * U) {
-        uint4 wa[U][RT], wb[U][RT];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int kk = k0 + u * 32 + t * 8;
-            const bool ok = kk < kend;
-#pragma unroll
-            for (int r = 0; r < RT; ++r) {
-                wa[u][r] = ok ? ldg_stream(wrow_a[r] + kk) : zero;
-                wb[u][r] = ok ? ldg_stream(wrow_b[r] + kk) : zero;
+    // The weights are constant, so everything that touches only W happens before the wait on the
+    // preceding kernel (whose output is A) and overlaps its tail: the first U steps are loaded into
+    // registers and the rest of this warp's range is pulled into L2.
+    uint4 wa[U][RT], wb[U][RT], xa[U][NT];
+
+#define SKINNY_LOAD(KBASE)                                                 \
+    _Pragma("unroll") for (int u = 0; u < U; ++u) {                        \
+        const int kk = (KBASE) + u * 32 + t * 8;                           \
+        const bool ok = kk < kend;                                         \
+        _Pragma("unroll") for (int r = 0; r < RT; ++r) {                   \
+            wa[u][r] = ok ? ldg_stream(wrow_a[r] + kk) : zero;             \
+            wb[u][r] = ok ? ldg_stream(wrow_b[r] + kk) : zero;             \
+        }                                                                  \
+    }
+    // activations of the same steps, issued right behind the weights so both are in flight together
+#define SKINNY_LOAD_A(KBASE)                                                        \
+    _Pragma("unroll") for (int u = 0; u < U; ++u) {                                 \
+        const int kk = (KBASE) + u * 32 + t * 8;                                    \
+        const bool ok = kk < kend;                                                  \
+        _Pragma("unroll") for (int n = 0; n < NT; ++n)                              \
+            xa[u][n] = (ok && arow_ok[n]) ? ldg_plain(arow[n] + kk) : zero;         \
+    }
+
+    pdl_trigger();
+    SKINNY_LOAD(kbeg)
+    {
+        const int kpre = kbeg + 32 * U;                     // multiple of 32 elements = 64 bytes
+        if (prefetch && kpre < kend) {
+            const int lines = (kend - kpre + 63) / 64;      // 128-byte lines per row
+            for (int idx = lane; idx < R * lines; idx += 32) {
+                const int r = idx / lines, line = idx - r * lines;
+                const int row = min(row0 + r, N - 1);
+                const bf16* p = W + (size_t)row * ldw + kpre + line * 64;
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
             }
         }
+    }
+    pdl_wait();
+    for (int k0 = kbeg; k0 < kend; k0 += 32 * U) {
+        if (k0 != kbeg) {
+            SKINNY_LOAD(k0)
+        }
+        SKINNY_LOAD_A(k0)
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int kk = k0 + u * 32 + t * 8;
-            const bool ok = kk < kend;
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
-                const uint4 x = (ok && arow_ok[n]) ? ldg_cached(arow[n] + kk) : zero;
 #pragma unroll
                 for (int r = 0; r < RT; ++r) {
-                    mma_bf16_16816(acc[r][n], wa[u][r].x, wb[u][r].x, wa[u][r].y, wb[u][r].y, x.x, x.y);
-                    mma_bf16_16816(acc[r][n], wa[u][r].z, wb[u][r].z, wa[u][r].w, wb[u][r].w, x.z, x.w);
+                    mma_bf16_16816(acc[r][n], wa[u][r].x, wb[u][r].x, wa[u][r].y, wb[u][r].y, xa[u][n].x, xa[u][n].y);
+                    mma_bf16_16816(acc[r][n], wa[u][r].z, wb[u][r].z, wa[u][r].w, wb[u][r].w, xa[u][n].z, xa[u][n].w);
                 }
             }
         }
     }
+#undef SKINNY_LOAD_A
+#undef SKINNY_LOAD
 
     // partial sums of this warp -> shared memory.  c0:(row g, col 2t) c1:(g, 2t+1) c2:(g+8, 2t) c3:(g+8, 2t+1)
     float* mine = red + (size_t)warp * R * RS;
@@ -142,26 +176,55 @@ __global__ void skinny_gemm_kernel(const bf16* __restrict__ A, long lda, const b
         }
     __syncthreads();
 
+    // With K split between blocks, each block leaves its [rows x M] partial in `scratch`; the last
+    // block of a tile to arrive (a counter per tile, no waiting) adds the partials in split order,
+    // so the sum does not depend on which block came last.
+    const float* src = red;
+    int n_src = n_warps;
+    size_t src_stride = (size_t)R * RS;
+    if (ksplit > 1) {
+        __shared__ int s_last;
+        float* mine_g = scratch + ((size_t)blockIdx.x * ksplit + blockIdx.y) * R * RS;
+        for (int idx = threadIdx.x; idx < R * MP; idx += blockDim.x) {
+            const int m = idx / R, r = idx - m * R;
+            float v = 0.0f;
+            for (int w = 0; w < n_warps; ++w) v += red[((size_t)w * R + r) * RS + m];
+            mine_g[r * RS + m] = v;
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) s_last = atomicAdd(&counters[blockIdx.x], 1) == ksplit - 1;
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+        if (threadIdx.x == 0) counters[blockIdx.x] = 0;       // ready for the next launch
+        src = scratch + (size_t)blockIdx.x * ksplit * R * RS;
+        n_src = ksplit;
+    }
+    auto total = [&](int r, int m) {
+        float v = 0.0f;
+        if (ksplit > 1) {
+            for (int w = 0; w < n_src; ++w) v += __ldcg(src + (size_t)w * src_stride + r * RS + m);
+        } else {
+            for (int w = 0; w < n_src; ++w) v += src[(size_t)w * src_stride + r * RS + m];
+        }
+        return v;
+    };
+
     if (epilogue == EPI_SWIGLU) {
         constexpr int PAIRS = R / 2;
         for (int idx = threadIdx.x; idx < PAIRS * MP; idx += blockDim.x) {
             const int m = idx / PAIRS, p = idx - m * PAIRS;
             const int row = row0 + 2 * p;
             if (m >= M || row + 1 >= N) continue;
-            float gate = 0.0f, up = 0.0f;
-            for (int w = 0; w < n_warps; ++w) {
-                gate += red[((size_t)w * R + 2 * p) * RS + m];
-                up += red[((size_t)w * R + 2 * p + 1) * RS + m];
-            }
-            store_from_f32(C, c_dtype, (size_t)m * ldc + (row >> 1), silu_mul_fast(gate, up));
+            store_from_f32(C, c_dtype, (size_t)m * ldc + (row >> 1), silu_mul_fast(total(2 * p, m), total(2 * p + 1, m)));
         }
     } else {
         for (int idx = threadIdx.x; idx < R * MP; idx += blockDim.x) {
             const int m = idx / R, r = idx - m * R;
             const int row = row0 + r;
             if (m >= M || row >= N) continue;
-            float v = 0.0f;
-            for (int w = 0; w < n_warps; ++w) v += red[((size_t)w * R + r) * RS + m];
+            const float v = total(r, m);
             const size_t o = (size_t)m * ldc + row;
             if (epilogue == EPI_ACCUMULATE)
                 reinterpret_cast<float*>(C)[o] += v;
@@ -171,32 +234,84 @@ __global__ void skinny_gemm_kernel(const bf16* __restrict__ A, long lda, const b
     }
 }
 
+// Tuning overrides for experiments: 0 keeps the built-in choice.
+static int g_tune_warps = 0;
+static int g_tune_prefetch = 0;
+static int g_tune_ksplit = 0;
+extern "C" int bfi_skinny_tune(int warps, int prefetch, int ksplit) {
+    g_tune_warps = warps;
+    g_tune_prefetch = prefetch;
+    g_tune_ksplit = ksplit;
+    return 0;
+}
+
+// The plan of a launch: warps per block, split of K between blocks, scratch it needs.
+struct SkinnyPlan {
+    int tiles, warps, ksplit, k_per_warp;
+    size_t smem;
+    long scratch_floats;
+    int counters;
+};
+
+static SkinnyPlan plan_skinny(int rows_per_tile, int m_pad, int N, int K, bool allow_split) {
+    SkinnyPlan p;
+    p.tiles = (N + rows_per_tile - 1) / rows_per_tile;
+    // many tiles: small blocks, several per SM; few tiles: wider blocks and K split between blocks
+    p.warps = p.tiles >= 600 ? 4 : 8;
+    if (g_tune_warps > 0) p.warps = g_tune_warps;
+    while (p.warps > 1 && K / p.warps < 64) p.warps >>= 1;
+    p.ksplit = 1;
+    if (allow_split && p.tiles < 300) {
+        p.ksplit = (296 + p.tiles - 1) / p.tiles;       // about two blocks per SM
+        while (p.ksplit > 1 && K / (p.ksplit * p.warps) < 128) --p.ksplit;
+    }
+    if (g_tune_ksplit > 0 && allow_split) p.ksplit = g_tune_ksplit;
+    int per = (K + p.ksplit * p.warps - 1) / (p.ksplit * p.warps);
+    p.k_per_warp = ((per + 31) / 32) * 32;
+    p.smem = (size_t)p.warps * rows_per_tile * (m_pad + 1) * sizeof(float);
+    p.scratch_floats = p.ksplit > 1 ? (long)p.tiles * p.ksplit * rows_per_tile * (m_pad + 1) : 0;
+    p.counters = p.ksplit > 1 ? p.tiles : 0;
+    return p;
+}
+
 template <int NT, int RT, int U>
 static int launch_skinny(const bf16* A, long lda, const bf16* W, long ldw, void* C, int c_dtype, long ldc, int M, int N,
-                         int K, int epilogue, cudaStream_t stream) {
+                         int K, int epilogue, float* scratch, long scratch_floats, int* counters, int n_counters,
+                         cudaStream_t stream) {
     constexpr int R = RT * 16;
-    const int tiles = (N + R - 1) / R;
-    // enough warps to keep ~16 per SM busy, each with at least 4 steps of 32 k
-    int warps = 8;
-    if ((long)tiles * 8 < 148L * 12 && K >= 16 * 128) warps = 16;
-    while (warps > 1 && K / warps < 64) warps >>= 1;
-    int k_per_warp = (K + warps - 1) / warps;
-    k_per_warp = ((k_per_warp + 31) / 32) * 32;
-    const size_t smem = (size_t)warps * R * (NT * 8 + 1) * sizeof(float);
+    SkinnyPlan p = plan_skinny(R, NT * 8, N, K, scratch != nullptr && counters != nullptr);
+    if (p.ksplit > 1 && (p.scratch_floats > scratch_floats || p.counters > n_counters))
+        return bfi_fail("skinny_gemm: scratch too small: need %ld floats and %d counters, got %ld and %d",
+                        p.scratch_floats, p.counters, scratch_floats, n_counters);
     auto kernel = skinny_gemm_kernel<NT, RT, U>;
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return bfi_fail("skinny_gemm: cannot reserve %zu bytes of shared memory: %s", smem,
+    if (p.smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
+        if (e != cudaSuccess) return bfi_fail("skinny_gemm: cannot reserve %zu bytes of shared memory: %s", p.smem,
                                               cudaGetErrorString(e));
     }
-    kernel<<<tiles, warps * 32, smem, stream>>>(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, k_per_warp, epilogue);
+    bfi_launch(kernel, dim3(p.tiles, p.ksplit), dim3(p.warps * 32), p.smem, stream, A, lda, W, ldw, C, c_dtype, ldc, M, N,
+               K, p.k_per_warp, epilogue, g_tune_prefetch, p.ksplit, scratch, counters);
     return bfi_check_launch("skinny_gemm");
+}
+
+static inline bool skinny_wide(int M, int N) { return N >= 9600 && M <= 32; }
+static inline int skinny_nt(int M) { return M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8)); }
+
+// Scratch a call may use: sizes[0] floats, sizes[1] int counters (which must start at zero and are
+// left at zero by every call).  Zero means the shape never splits K.
+extern "C" int bfi_skinny_gemm_scratch(int M, int N, int K, long* sizes) {
+    const int rows = skinny_wide(M, N) ? 32 : 16;
+    SkinnyPlan p = plan_skinny(rows, skinny_nt(M) * 8, N, K, true);
+    sizes[0] = p.scratch_floats;
+    sizes[1] = p.counters;
+    return 0;
 }
 
 // Returns 0 on success, 1 on error, and 2 when the shape is not taken (nothing launched; the
 // caller uses the general kernel).
 extern "C" int bfi_skinny_gemm_bf16(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype, long ldc,
-                                    int M, int N, int K, int epilogue, cudaStream_t stream) {
+                                    int M, int N, int K, int epilogue, float* scratch, long scratch_floats,
+                                    int* counters, int n_counters, cudaStream_t stream) {
     BFI_REQUIRE(dtype_ok(c_dtype), "skinny_gemm: unknown output dtype code %d", c_dtype);
     BFI_REQUIRE(M >= 0 && N > 0 && K > 0, "skinny_gemm: bad sizes M=%d N=%d K=%d", M, N, K);
     BFI_REQUIRE(epilogue >= 0 && epilogue <= 2, "skinny_gemm: unknown epilogue %d", epilogue);
@@ -207,13 +322,16 @@ extern "C" int bfi_skinny_gemm_bf16(const void* A, long lda, const void* W, long
     if (M > 64 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return 2;
     const bf16* a = (const bf16*)A;
     const bf16* w = (const bf16*)W;
-    const bool wide = N >= 9600;   // many rows: two m-tiles per block halve the activation traffic
-#define BFI_SKINNY(NT, U)                                                                                          \
-    return wide ? launch_skinny<NT, 2, U>(a, lda, w, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream)              \
-                : launch_skinny<NT, 1, U>(a, lda, w, ldw, C, c_dtype, ldc, M, N, K, epilogue, stream);
-    if (M <= 8) { BFI_SKINNY(1, 4) }
-    if (M <= 16) { BFI_SKINNY(2, 4) }
-    if (M <= 32) { BFI_SKINNY(4, 2) }
-    BFI_SKINNY(8, 2)
+    const bool wide = skinny_wide(M, N);   // many rows: two m-tiles per block halve the activation traffic
+#define BFI_SKINNY(NT, U1, U2)                                                                                     \
+    return wide ? launch_skinny<NT, 2, U2>(a, lda, w, ldw, C, c_dtype, ldc, M, N, K, epilogue, scratch,            \
+                                           scratch_floats, counters, n_counters, stream)                           \
+                : launch_skinny<NT, 1, U1>(a, lda, w, ldw, C, c_dtype, ldc, M, N, K, epilogue, scratch,            \
+                                           scratch_floats, counters, n_counters, stream);
+    if (M <= 8) { BFI_SKINNY(1, 4, 4) }
+    if (M <= 16) { BFI_SKINNY(2, 4, 4) }
+    if (M <= 32) { BFI_SKINNY(4, 2, 2) }
+    return launch_skinny<8, 1, 2>(a, lda, w, ldw, C, c_dtype, ldc, M, N, K, epilogue, scratch, scratch_floats, counters,
+                                  n_counters, stream);
 #undef BFI_SKINNY
 }

@@ -14,6 +14,48 @@ SKINNY_MAX_ROWS = 64
 SM_COUNT = 148
 
 
+class _SplitScratch:
+    """Scratch of the weight streamer when it splits K between blocks: float32 partial sums and one
+    counter per tile.  The counters start at zero and every launch leaves them at zero.  Buffers
+    only ever grow, and outgrown ones are kept alive, because captured graphs hold their addresses.
+    One stream at a time may use them."""
+
+    def __init__(self):
+        self.floats = {}
+        self.counters = {}
+        self.retired = []
+
+    def get(self, device, n_floats: int, n_counters: int):
+        f = self.floats.get(device)
+        if f is None or f.numel() < n_floats:
+            if f is not None:
+                self.retired.append(f)
+            f = torch.empty(max(n_floats, 1 << 20), dtype=torch.float32, device=device)
+            self.floats[device] = f
+        c = self.counters.get(device)
+        if c is None or c.numel() < n_counters:
+            if c is not None:
+                self.retired.append(c)
+            c = torch.zeros(max(n_counters, 1 << 14), dtype=torch.int32, device=device)
+            self.counters[device] = c
+        return f, c
+
+
+_split_scratch = _SplitScratch()
+_plan_cache = {}
+
+
+def _skinny_scratch_need(m: int, n: int, k: int):
+    key = (m, n, k)
+    need = _plan_cache.get(key)
+    if need is None:
+        sizes = (c_long * 2)()
+        library("fast").lib.bfi_skinny_gemm_scratch(c_int(m), c_int(n), c_int(k), sizes)
+        need = (int(sizes[0]), int(sizes[1]))
+        _plan_cache[key] = need
+    return need
+
+
 def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int) -> bool:
     """bfloat16 x bfloat16 -> ``out`` (float32 or bfloat16).  Few rows: the weight streamer."""
     m, k = a.shape
@@ -26,9 +68,15 @@ def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
     cols = n // 2 if epilogue == 2 else n
     if w.shape[1] != k or out.shape != (m, cols):
         raise KernelError(f"matrix product: A {tuple(a.shape)}, W {tuple(w.shape)}, output {tuple(out.shape)}")
+    n_floats, n_counters = _skinny_scratch_need(m, n, k)
+    scratch = counters = None
+    if n_floats:
+        scratch, counters = _split_scratch.get(a.device, n_floats, n_counters)
     return library("fast").call_optional(
         "bfi_skinny_gemm_bf16", _ptr(a), c_long(a.stride(0)), _ptr(w), c_long(w.stride(0)), _ptr(out),
-        c_int(dtype_code(out.dtype)), c_long(out.stride(0)), c_int(m), c_int(n), c_int(k), c_int(epilogue), _stream())
+        c_int(dtype_code(out.dtype)), c_long(out.stride(0)), c_int(m), c_int(n), c_int(k), c_int(epilogue),
+        _ptr(scratch), c_long(scratch.numel() if scratch is not None else 0), _ptr(counters),
+        c_int(counters.numel() if counters is not None else 0), _stream())
 
 
 def decode_splits(n_seqs: int, n_kv: int, group: int, max_pages: int) -> int:

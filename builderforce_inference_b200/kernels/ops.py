@@ -189,14 +189,21 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int
                          c_long(out.stride(0)), c_int(m), c_int(n), c_int(k), c_int(epilogue), _stream())
 
 
-def argmax_rows(logits: torch.Tensor, out: torch.Tensor) -> None:
-    _need_cuda(logits, out)
+def argmax_rows(logits: torch.Tensor, out: torch.Tensor, scratch: Optional[torch.Tensor] = None) -> None:
+    """``scratch`` (int32 or float32, at least ``2 * rows * ceil(vocab / 8192)`` values) lets many
+    blocks search each row of a large vocabulary."""
+    _need_cuda(logits, out, scratch)
     _rows_2d(logits, "logits")
     _i32(out, "argmax output")
     if logits.dtype != torch.float32 or out.numel() < logits.shape[0]:
         raise KernelError("argmax: logits must be float32 and the output hold one id per row")
+    n_scratch = 0
+    if scratch is not None:
+        if scratch.element_size() != 4 or not scratch.is_contiguous():
+            raise KernelError("argmax: scratch must be a contiguous tensor of 4-byte values")
+        n_scratch = scratch.numel()
     library("core").call("bfi_argmax_rows", _ptr(logits), c_long(logits.stride(0)), c_int(logits.shape[0]),
-                         c_int(logits.shape[1]), _ptr(out), _stream())
+                         c_int(logits.shape[1]), _ptr(out), _ptr(scratch), c_long(n_scratch), _stream())
 
 
 def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, u: torch.Tensor, out: torch.Tensor,

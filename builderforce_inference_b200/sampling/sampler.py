@@ -47,6 +47,7 @@ class Sampler:
         self.vocab = vocab_size
         self._out = torch.empty(0, dtype=torch.int32, device=device)
         self._work: Optional[torch.Tensor] = None
+        self._scratch = torch.empty(0, dtype=torch.int32, device=device)
 
     def _out_rows(self, n: int) -> torch.Tensor:
         if self._out.numel() < n:
@@ -62,7 +63,10 @@ class Sampler:
         if rows == 0:
             return out
         if params.greedy and not params.has_penalties:
-            ops.argmax_rows(logits, out)
+            need = 2 * rows * ((self.vocab + 8191) // 8192)
+            if self._scratch.numel() < need:
+                self._scratch = torch.empty(2 * need, dtype=torch.int32, device=self.device)
+            ops.argmax_rows(logits, out, self._scratch)
             return out
         u = [uniform_draw(params.seed, r, s) for r, s in zip(requests, steps)]
         seen = seen_cu = work = None

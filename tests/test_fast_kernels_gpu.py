@@ -133,3 +133,22 @@ def test_attention_decode_declines_other_head_sizes():
     pages = Pages(1, 64, 1, 48, torch.bfloat16)
     q = torch.zeros(1, 48, dtype=torch.bfloat16, device=DEV)
     assert not fast().attention_decode_bf16(Ctx([0], [3]), q, torch.empty_like(q), pages.view, 1, 0.1)
+
+
+@pytest.mark.parametrize("m", [1, 8, 24, 64])
+def test_skinny_gemm_splits_k_between_blocks_and_stays_deterministic(m):
+    """Few row tiles and a long K: blocks share K and the last to arrive adds their partial sums in
+    a fixed order, so two runs agree to the bit and the counters are left at zero."""
+    n, k = 2560, 4096
+    a = torch.randn(m, k, generator=gen(m)).bfloat16().to(DEV)
+    w = (torch.randn(n, k, generator=gen(5)) * 0.05).bfloat16().to(DEV)
+    assert fast()._skinny_scratch_need(m, n, k)[0] > 0          # this shape does split
+    res = torch.randn(m, n, generator=gen(6))
+    outs = []
+    for _ in range(3):
+        out = res.clone().to(DEV)
+        assert fast().linear_bf16(a, w, out, 1)
+        outs.append(out.cpu())
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    assert rel_err(outs[0], res + P.linear(w.float().cpu(), a.float().cpu())) < 2e-5
+    assert int(fast()._split_scratch.counters[a.device].abs().sum()) == 0

@@ -357,6 +357,11 @@ def test_argmax_lowest_index_wins_and_any_vocabulary():
         ops().argmax_rows(x.to(DEV), out)
         assert out.tolist() == [vocab // 2, 0, 0]
         assert out.tolist()[:2] == [P.argmax_first(r.tolist()) for r in x[:2]]
+        # with scratch, many blocks search each row; same answers, ties across chunks included
+        scratch = torch.empty(2 * 3 * (vocab // 8192 + 1), dtype=torch.int32, device=DEV)
+        out.fill_(-1)
+        ops().argmax_rows(x.to(DEV), out, scratch)
+        assert out.tolist() == [vocab // 2, 0, 0]
 
 
 @pytest.mark.parametrize("vocab", [37, 384, 5000])

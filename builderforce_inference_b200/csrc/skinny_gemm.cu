@@ -335,3 +335,58 @@ extern "C" int bfi_skinny_gemm_bf16(const void* A, long lda, const void* W, long
                                   n_counters, stream);
 #undef BFI_SKINNY
 }
+
+// ------------------------------------------------------------------------------------------
+// The same product for callers that cannot allocate: scratch in the library's own device image.
+// See no_alloc.h for the contract.
+// ------------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+static __device__ __align__(256) float bfi_static_scratch[BFI_STATIC_SCRATCH_FLOATS];
+
+#define BFI_MAX_DEVICES 64
+static float* g_static_scratch_addr[BFI_MAX_DEVICES] = {nullptr};
+
+// The array's name is only a host-side handle; kernels need its address on the current device.
+static int static_scratch_address(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return bfi_fail("skinny_gemm_static: cudaGetDevice failed: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= BFI_MAX_DEVICES) return bfi_fail("skinny_gemm_static: device index %d out of range", dev);
+    if (g_static_scratch_addr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, bfi_static_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return bfi_fail("skinny_gemm_static: cannot find the scratch array on device %d: %s", dev,
+                            cudaGetErrorString(e));
+        g_static_scratch_addr[dev] = static_cast<float*>(p);
+    }
+    *out = g_static_scratch_addr[dev];
+    return 0;
+}
+
+extern "C" int bfi_skinny_gemm_bf16_static(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype,
+                                           long ldc, int M, int N, int K, int epilogue, cudaStream_t stream) {
+    BFI_REQUIRE(M >= 0 && N > 0 && K > 0, "skinny_gemm_static: bad sizes M=%d N=%d K=%d", M, N, K);
+    if (M == 0) return 0;
+    if (M > 64) return 2;
+    long need[2] = {0, 0};
+    bfi_skinny_gemm_scratch(M, N, K, need);
+    const long room = (long)BFI_STATIC_SCRATCH_FLOATS - BFI_STATIC_COUNTER_SLOTS;
+    BFI_REQUIRE(need[0] <= room && need[1] <= BFI_STATIC_COUNTER_SLOTS,
+                "skinny_gemm_static: M=%d N=%d K=%d needs %ld floats of scratch and %ld counters; the built-in array "
+                "holds %ld and %d",
+                M, N, K, need[0], need[1], room, BFI_STATIC_COUNTER_SLOTS);
+    float* base = nullptr;
+    int rc = static_scratch_address(&base);
+    if (rc) return rc;
+    int* counters = reinterpret_cast<int*>(base);
+    float* partials = base + BFI_STATIC_COUNTER_SLOTS;
+    if (need[1] > 0) {
+        // whatever an earlier call left behind, the counters of this call start at zero
+        cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)need[1] * sizeof(int), stream);
+        if (e != cudaSuccess) return bfi_fail("skinny_gemm_static: clearing the counters failed: %s", cudaGetErrorString(e));
+    }
+    return bfi_skinny_gemm_bf16(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, partials, room, counters,
+                                BFI_STATIC_COUNTER_SLOTS, stream);
+}

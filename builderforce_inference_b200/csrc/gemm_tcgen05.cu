@@ -1,0 +1,520 @@
+// bfloat16 matrix product on the fifth-generation tensor cores: C[M,N] = A[M,K] * W[N,K]^T with
+// float32 accumulation in tensor memory.
+//
+// The roles are swapped with respect to the textbook GEMM: 128 rows of W are the M side of
+// tcgen05.mma (one TMEM lane per output feature) and BT tokens are its N side (one TMEM column
+// per token), so the same kernel serves prompts (BT = 256 tokens per tile) and decode batches
+// (BT = 16..64), where the work is streaming W once: a ring of up to ten 16 KB weight tiles per
+// SM is kept in flight by TMA.
+//
+//   warp 0     one lane issues the TMA loads of W and A tiles (128-byte swizzle) into the ring
+//   warp 1     allocates tensor memory; one lane issues tcgen05.mma (4 per 64-wide k block) and
+//              commits each block to the ring's "empty" barrier, the last one to "tmem_full"
+//   warps 2-5  epilogue: tcgen05.ld of their 32 lanes, then store / add into the float32 residual /
+//              SiLU(gate)*up over interleaved rows.  With K split, the blocks of one tile form a
+//              thread-block cluster: each leaves its partial tile in its own shared memory and
+//              then adds, in split order, a share of the tile's tokens out of all the blocks'
+//              shared memory (distributed shared memory), so nothing goes through global scratch
+//              and the sum does not depend on timing
+//
+// Every wait on an mbarrier is bounded: a wait that runs out records BFI_STATUS_TIMEOUT in the
+// status word, and the block drains its copies, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+#define EPI_STORE 0
+#define EPI_ACCUMULATE 1
+#define EPI_SWIGLU 2
+
+#define BFI_STATUS_TIMEOUT 8
+
+#define TC_ROWS 128           // W rows per tile (UMMA M)
+#define TC_BK 64              // k elements per stage: one 128-byte swizzle row
+#define TC_THREADS 192
+#define TC_SPIN_LIMIT (1u << 22)
+
+// ------------------------------------------------------------------------------------------
+// PTX wrappers
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols));
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols));
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart (SBO), version 1, layout type 2.  `addr` may point 32, 64 or
+// 96 bytes into a row to select a 16-element k slice.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);          // start address, bits [0,14)
+    d |= (uint64_t)1 << 16;                          // leading byte offset (unused with swizzle), bits [16,30)
+    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset, bits [32,46)
+    d |= (uint64_t)1 << 46;                          // descriptor version for sm_100
+    d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor, kind::f16: D float32, A and B bfloat16, both K-major, M x N.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ float silu_mul_tc(float g, float u) {
+    float s;
+    if (g >= 0.0f) {
+        s = 1.0f / (1.0f + __expf(-g));
+    } else {
+        const float z = __expf(g);
+        s = z / (1.0f + z);
+    }
+    return g * s * u;
+}
+
+template <int BT>
+struct TcConfig {
+    static constexpr int STAGE_BYTES = TC_ROWS * TC_BK * 2 + BT * TC_BK * 2;
+    // few tokens per tile (decode): two blocks share an SM, each with a ring of ~110 KB, so that a
+    // grid a little larger than the SM count still runs in one wave; many tokens: one block per SM
+    static constexpr int BUDGET = BT <= 64 ? 110 * 1024 : 196 * 1024;
+    static constexpr int STAGES = BUDGET / STAGE_BYTES;
+    static constexpr int BLOCKS_PER_SM = BT <= 64 ? 2 : 1;
+    static constexpr int TMEM_COLS = BT < 32 ? 32 : BT;
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+};
+
+// ------------------------------------------------------------------------------------------
+// The kernel.  grid = (row tiles of W, token tiles, splits of K)
+// ------------------------------------------------------------------------------------------
+template <int BT>
+__global__ void __launch_bounds__(TC_THREADS, TcConfig<BT>::BLOCKS_PER_SM)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+                    void* __restrict__ C, int c_dtype, long ldc, int M, int N, int K, int kblocks_per_split,
+                    int epilogue, int* __restrict__ status) {
+    using Cfg = TcConfig<BT>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES);
+    uint64_t* empty = full + Cfg::STAGES;
+    uint64_t* tmem_full = empty + Cfg::STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+    int* s_flag = reinterpret_cast<int*>(tmem_slot + 1);      // [0] error seen, [1] this block reduces the splits
+
+    pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * TC_ROWS;
+    const int m0 = blockIdx.y * BT;
+    const int total_kblocks = (K + TC_BK - 1) / TC_BK;
+    const int kb_beg = blockIdx.z * kblocks_per_split;
+    const int kb_end = min(total_kblocks, kb_beg + kblocks_per_split);
+    const int n_kb = max(0, kb_end - kb_beg);
+    const int ksplit = gridDim.z;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(tmem_full, 1);
+        s_flag[0] = 0;
+        s_flag[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();
+
+    if (warp == 0) {
+        // ---------------- TMA producer
+        if (lane == 0) {
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % Cfg::STAGES;
+                const uint32_t phase = (i / Cfg::STAGES) & 1;
+                if (i >= Cfg::STAGES && !mbar_wait(&empty[s], phase ^ 1)) {
+                    atomicOr(status, BFI_STATUS_TIMEOUT);
+                    s_flag[0] = 1;
+                    break;
+                }
+                unsigned char* stage = smem + (size_t)s * Cfg::STAGE_BYTES;
+                mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+                const int k = (kb_beg + i) * TC_BK;
+                tma_load_2d(stage, &map_w, k, n0, &full[s]);
+                tma_load_2d(stage + TC_ROWS * TC_BK * 2, &map_a, k, m0, &full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(TC_ROWS, BT);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % Cfg::STAGES;
+                const uint32_t phase = (i / Cfg::STAGES) & 1;
+                if (!mbar_wait(&full[s], phase)) {
+                    atomicOr(status, BFI_STATUS_TIMEOUT);
+                    s_flag[0] = 1;
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t wa = smem_u32(smem + (size_t)s * Cfg::STAGE_BYTES);
+                const uint32_t aa = wa + TC_ROWS * TC_BK * 2;
+#pragma unroll
+                for (int kk = 0; kk < TC_BK / 16; ++kk)
+                    umma_bf16(tmem_base, umma_desc_sw128(wa + kk * 32), umma_desc_sw128(aa + kk * 32), idesc,
+                              (i > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(&empty[s]);          // the stage is free once these MMAs have read it
+            }
+            umma_commit(tmem_full);               // arrives when every MMA issued above has completed
+        }
+    } else {
+        // ---------------- epilogue warps: TMEM lanes 32*(warp % 4) .. +31
+        const int quad = warp & 3;
+        const int n_local = quad * 32 + lane;
+        const int n = n0 + n_local;
+        bool ok = true;
+        if (n_kb > 0) {
+            ok = mbar_wait(tmem_full, 0);
+            if (!ok && lane == 0) {
+                atomicOr(status, BFI_STATUS_TIMEOUT);
+                s_flag[0] = 1;
+            }
+        }
+        tc_fence_after();
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+
+        if (ksplit > 1) {
+            // partial tile -> this block's shared memory as [token][row] (the ring is idle by now)
+            float* part = reinterpret_cast<float*>(smem);
+#pragma unroll 1
+            for (int c = 0; c < BT / 16; ++c) {
+                float v[16];
+                if (ok && n_kb > 0) {
+                    tmem_ld16(lane_addr + c * 16, v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) part[(c * 16 + j) * TC_ROWS + n_local] = v[j];
+            }
+        } else if (ok) {
+#pragma unroll 1
+            for (int c = 0; c < BT / 16; ++c) {
+                if (m0 + c * 16 >= M) break;
+                float v[16];
+                tmem_ld16(lane_addr + c * 16, v);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int m = m0 + c * 16 + j;
+                    if (epilogue == EPI_SWIGLU) {
+                        const float up = __shfl_down_sync(0xffffffffu, v[j], 1);
+                        if (m < M && (lane & 1) == 0 && n + 1 < N)
+                            store_from_f32(C, c_dtype, (size_t)m * ldc + (n >> 1), silu_mul_tc(v[j], up));
+                    } else if (m < M && n < N) {
+                        const size_t o = (size_t)m * ldc + n;
+                        if (epilogue == EPI_ACCUMULATE)
+                            reinterpret_cast<float*>(C)[o] += v[j];
+                        else
+                            store_from_f32(C, c_dtype, o, v[j]);
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------- split K: the cluster's blocks add their partial tiles
+    if (ksplit > 1) {
+        __syncwarp();
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (warp >= 2) {
+            const int quad = warp & 3;
+            const int n_local = quad * 32 + lane;
+            const int n = n0 + n_local;
+            const int rank = blockIdx.z;                         // cluster dims are (1, 1, ksplit)
+            const int per_rank = (BT + ksplit - 1) / ksplit;     // tokens this block finishes
+            const uint32_t local = smem_u32(smem);
+            for (int j = rank * per_rank; j < min(BT, (rank + 1) * per_rank); ++j) {
+                const int m = m0 + j;
+                if (m >= M) break;
+                float v = 0.0f;
+                for (int r = 0; r < ksplit; ++r) {
+                    uint32_t remote;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(r));
+                    float x;
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(x) : "r"(remote + (uint32_t)(j * TC_ROWS + n_local) * 4));
+                    v += x;
+                }
+                if (epilogue == EPI_SWIGLU) {
+                    const float up = __shfl_down_sync(0xffffffffu, v, 1);
+                    if ((lane & 1) == 0 && n + 1 < N)
+                        store_from_f32(C, c_dtype, (size_t)m * ldc + (n >> 1), silu_mul_tc(v, up));
+                } else if (n < N) {
+                    const size_t o = (size_t)m * ldc + n;
+                    if (epilogue == EPI_ACCUMULATE)
+                        reinterpret_cast<float*>(C)[o] += v;
+                    else
+                        store_from_f32(C, c_dtype, o, v);
+                }
+            }
+        }
+        // no block may leave while another still reads its shared memory
+        __syncwarp();
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
+
+    // ---------------- common tail: everyone meets, copies in flight are drained, TMEM is freed
+    tc_fence_before();
+    __syncthreads();
+    if (s_flag[0] && warp == 0 && lane == 0) {
+        // a wait ran out: let outstanding TMA writes land (bounded) before the block's memory is reused
+        for (int s = 0; s < Cfg::STAGES && s < n_kb; ++s) {
+            const int last = ((n_kb - 1 - s) / Cfg::STAGES) * Cfg::STAGES + s;   // last k block that used stage s
+            mbar_wait(&full[s], (uint32_t)((last / Cfg::STAGES) & 1));
+        }
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Host side: tensor maps (cached), planning, launch
+// ------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr;
+    long rows, cols, ld;
+    int box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = std::hash<const void*>()(k.ptr);
+        h = h * 1000003u ^ std::hash<long>()(k.rows);
+        h = h * 1000003u ^ std::hash<long>()(k.cols);
+        h = h * 1000003u ^ std::hash<long>()(k.ld);
+        return h * 1000003u ^ std::hash<int>()(k.box_rows);
+    }
+};
+static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+static std::mutex g_maps_mutex;
+
+// A [rows, cols] bfloat16 matrix with row stride ld (elements), read in boxes of box_rows x 64.
+static int tensor_map(const void* ptr, long rows, long cols, long ld, int box_rows, CUtensorMap* out) {
+    MapKey key{ptr, rows, cols, ld, box_rows};
+    std::lock_guard<std::mutex> lock(g_maps_mutex);
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) {
+        *out = it->second;
+        return 0;
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return bfi_fail("gemm_tcgen05: the driver does not export cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMap m;
+    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return bfi_fail("gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    if (g_maps.size() > 4096) g_maps.clear();
+    g_maps[key] = m;
+    *out = m;
+    return 0;
+}
+
+struct TcPlan {
+    int bt, tiles_n, tiles_m, ksplit, kblocks_per_split;
+};
+
+static int g_tc_tune_ksplit = 0;
+extern "C" int bfi_gemm_tcgen05_tune(int ksplit) {
+    g_tc_tune_ksplit = ksplit;
+    return 0;
+}
+
+static TcPlan plan_tc(int M, int N, int K) {
+    const bool allow_split = true;
+    TcPlan p;
+    p.bt = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)));
+    p.tiles_n = (N + TC_ROWS - 1) / TC_ROWS;
+    p.tiles_m = (M + p.bt - 1) / p.bt;
+    const int kblocks = (K + TC_BK - 1) / TC_BK;
+    p.ksplit = 1;
+    const long tiles = (long)p.tiles_n * p.tiles_m;
+    const long slots = p.bt <= 64 ? 296 : 148;          // blocks resident at once
+    if (allow_split && tiles * 2 <= slots) {
+        // few tiles: split K so that the grid fills the resident slots in one wave, with at least
+        // 8 k blocks per split (shorter runs cost more in fill and reduction than they gain)
+        int want = (int)(slots / tiles);
+        if (want > 8) want = 8;                         // portable cluster size
+        while (want > 1 && kblocks / want < 8) --want;
+        p.ksplit = want;
+    }
+    if (g_tc_tune_ksplit > 0) p.ksplit = g_tc_tune_ksplit > 8 ? 8 : g_tc_tune_ksplit;
+    p.kblocks_per_split = (kblocks + p.ksplit - 1) / p.ksplit;
+    p.ksplit = (kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split;   // no empty splits
+    return p;
+}
+
+template <int BT>
+static int launch_tc(const TcPlan& p, const CUtensorMap& mw, const CUtensorMap& ma, void* C, int c_dtype, long ldc,
+                     int M, int N, int K, int epilogue, int* status, cudaStream_t stream) {
+    using Cfg = TcConfig<BT>;
+    auto kernel = gemm_tcgen05_kernel<BT>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
+        if (e != cudaSuccess)
+            return bfi_fail("gemm_tcgen05: cannot reserve %zu bytes of shared memory: %s", Cfg::SMEM, cudaGetErrorString(e));
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.tiles_n, p.tiles_m, p.ksplit);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (p.ksplit > 1) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = 1;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = p.ksplit;
+        ++n_attr;
+    }
+    if (g_bfi_pdl) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mw, ma, C, c_dtype, ldc, M, N, K, p.kblocks_per_split, epilogue, status);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return bfi_fail("gemm_tcgen05: launch failed: %s", cudaGetErrorString(e));
+    }
+    return bfi_check_launch("gemm_tcgen05");
+}
+
+// Returns 0 on success, 1 on error, 2 when the shape is not taken (nothing launched).
+// `status` receives BFI_STATUS_TIMEOUT (8) if a bounded wait inside the kernel ran out.
+extern "C" int bfi_gemm_tcgen05_bf16(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype, long ldc,
+                                     int M, int N, int K, int epilogue, int* status, cudaStream_t stream) {
+    BFI_REQUIRE(dtype_ok(c_dtype), "gemm_tcgen05: unknown output dtype code %d", c_dtype);
+    BFI_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
+    BFI_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_tcgen05: unknown epilogue %d", epilogue);
+    BFI_REQUIRE(status != nullptr, "gemm_tcgen05: a status word is required");
+    if (epilogue == EPI_ACCUMULATE) BFI_REQUIRE(c_dtype == BFI_F32, "gemm_tcgen05: accumulation needs a float32 output");
+    if (epilogue == EPI_SWIGLU) BFI_REQUIRE(N % 2 == 0, "gemm_tcgen05: the gated epilogue needs an even N, got %d", N);
+    if (M == 0) return 0;
+    // TMA: 16-byte aligned bases and row strides
+    if (K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return 2;
+    TcPlan p = plan_tc(M, N, K);
+    if (p.tiles_m > 65535) return 2;
+    CUtensorMap mw, ma;
+    int rc = tensor_map(W, N, K, ldw, TC_ROWS, &mw);
+    if (rc) return rc;
+    rc = tensor_map(A, M, K, lda, p.bt, &ma);
+    if (rc) return rc;
+    switch (p.bt) {
+        case 16: return launch_tc<16>(p, mw, ma, C, c_dtype, ldc, M, N, K, epilogue, status, stream);
+        case 32: return launch_tc<32>(p, mw, ma, C, c_dtype, ldc, M, N, K, epilogue, status, stream);
+        case 64: return launch_tc<64>(p, mw, ma, C, c_dtype, ldc, M, N, K, epilogue, status, stream);
+        case 128: return launch_tc<128>(p, mw, ma, C, c_dtype, ldc, M, N, K, epilogue, status, stream);
+        default: return launch_tc<256>(p, mw, ma, C, c_dtype, ldc, M, N, K, epilogue, status, stream);
+    }
+}

@@ -195,6 +195,14 @@ class Engine:
 
     def check_status(self) -> None:
         bits = int(self.status.item())
+        if self.dtype == torch.bfloat16:
+            from ..kernels import fast_ops
+            tc = fast_ops.tc_status(self.device)
+            tc_bits = int(tc.item())
+            if tc_bits:
+                tc.zero_()
+                raise StepError("device-side check failed: a bounded wait in the tensor-core matrix product ran out "
+                                f"(status {tc_bits}); its results are not to be trusted")
         if bits:
             self.status.zero_()
             what = []

@@ -11,4 +11,4 @@ def attend(ctx, qkv, out, kv, n_heads: int, scale: float) -> bool:
     from . import fast_ops
     if ctx.max_seq_tokens == 1 and ctx.n_tokens == ctx.n_seqs:
         return fast_ops.attention_decode_bf16(ctx, qkv, out, kv, n_heads, scale)
-    return False
+    return fast_ops.attention_prefill_bf16(ctx, qkv, out, kv, n_heads, scale)

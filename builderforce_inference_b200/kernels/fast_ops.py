@@ -45,38 +45,86 @@ _split_scratch = _SplitScratch()
 _plan_cache = {}
 
 
-def _skinny_scratch_need(m: int, n: int, k: int):
-    key = (m, n, k)
-    need = _plan_cache.get(key)
-    if need is None:
-        sizes = (c_long * 2)()
-        library("fast").lib.bfi_skinny_gemm_scratch(c_int(m), c_int(n), c_int(k), sizes)
-        need = (int(sizes[0]), int(sizes[1]))
-        _plan_cache[key] = need
-    return need
+_tc_status = {}
 
 
-def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int) -> bool:
-    """bfloat16 x bfloat16 -> ``out`` (float32 or bfloat16).  Few rows: the weight streamer."""
+def tc_status(device) -> torch.Tensor:
+    """The word in which the tensor-core product records a bounded wait that ran out (bit 8)."""
+    t = _tc_status.get(device)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _tc_status[device] = t
+    return t
+
+
+def _check_product(a, w, out, epilogue):
     m, k = a.shape
     n = w.shape[0]
-    if m > SKINNY_MAX_ROWS:
-        return False
     _rows_2d(a, "A")
     _rows_2d(w, "W")
     _rows_2d(out, "C")
     cols = n // 2 if epilogue == 2 else n
     if w.shape[1] != k or out.shape != (m, cols):
         raise KernelError(f"matrix product: A {tuple(a.shape)}, W {tuple(w.shape)}, output {tuple(out.shape)}")
-    n_floats, n_counters = _skinny_scratch_need(m, n, k)
-    scratch = counters = None
-    if n_floats:
-        scratch, counters = _split_scratch.get(a.device, n_floats, n_counters)
+    return m, n, k
+
+
+def _scratch_for(func: str, m: int, n: int, k: int, device):
+    key = (func, m, n, k)
+    need = _plan_cache.get(key)
+    if need is None:
+        sizes = (c_long * 2)()
+        getattr(library("fast").lib, func)(c_int(m), c_int(n), c_int(k), sizes)
+        need = (int(sizes[0]), int(sizes[1]))
+        _plan_cache[key] = need
+    if need[0] == 0:
+        return None, None
+    return _split_scratch.get(device, need[0], need[1])
+
+
+def _skinny_scratch_need(m: int, n: int, k: int):
+    key = ("bfi_skinny_gemm_scratch", m, n, k)
+    if key not in _plan_cache:
+        sizes = (c_long * 2)()
+        library("fast").lib.bfi_skinny_gemm_scratch(c_int(m), c_int(n), c_int(k), sizes)
+        _plan_cache[key] = (int(sizes[0]), int(sizes[1]))
+    return _plan_cache[key]
+
+
+def skinny_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int) -> bool:
+    """The weight streamer (mma.sync), up to 64 rows."""
+    m, n, k = _check_product(a, w, out, epilogue)
+    if m > SKINNY_MAX_ROWS:
+        return False
+    scratch, counters = _scratch_for("bfi_skinny_gemm_scratch", m, n, k, a.device)
     return library("fast").call_optional(
         "bfi_skinny_gemm_bf16", _ptr(a), c_long(a.stride(0)), _ptr(w), c_long(w.stride(0)), _ptr(out),
         c_int(dtype_code(out.dtype)), c_long(out.stride(0)), c_int(m), c_int(n), c_int(k), c_int(epilogue),
         _ptr(scratch), c_long(scratch.numel() if scratch is not None else 0), _ptr(counters),
         c_int(counters.numel() if counters is not None else 0), _stream())
+
+
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int) -> bool:
+    """The tcgen05 / TMA kernel, any number of rows."""
+    m, n, k = _check_product(a, w, out, epilogue)
+    return library("fast").call_optional(
+        "bfi_gemm_tcgen05_bf16", _ptr(a), c_long(a.stride(0)), _ptr(w), c_long(w.stride(0)), _ptr(out),
+        c_int(dtype_code(out.dtype)), c_long(out.stride(0)), c_int(m), c_int(n), c_int(k), c_int(epilogue),
+        _ptr(tc_status(a.device)), _stream())
+
+
+TCGEN05_MIN_ROWS = 9      # fewer rows: the register-fed weight streamer
+
+
+def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int) -> bool:
+    """bfloat16 x bfloat16 -> ``out`` (float32 or bfloat16): the weight streamer for very few rows,
+    the tcgen05 kernel otherwise; False if neither takes the shape."""
+    m = a.shape[0]
+    if m >= TCGEN05_MIN_ROWS and gemm_tcgen05(a, w, out, epilogue):
+        return True
+    if m <= SKINNY_MAX_ROWS:
+        return skinny_gemm(a, w, out, epilogue)
+    return False
 
 
 def decode_splits(n_seqs: int, n_kv: int, group: int, max_pages: int) -> int:
@@ -103,3 +151,15 @@ def attention_decode_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads
         _ptr(kv.v), _ptr(kv.block_table), c_int(kv.block_table.stride(0)), _ptr(ctx.seq_slot), _ptr(ctx.seq_start),
         c_int(ctx.n_seqs), c_int(n_heads), c_int(kv.n_kv_heads), c_int(d), c_int(kv.window or 0), c_float(scale),
         c_int(splits), _ptr(part_o), _ptr(part_ml), _stream())
+
+
+def attention_prefill_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float) -> bool:
+    """Tensor-core attention for steps that bring more than one token per sequence."""
+    d = kv.head_dim
+    if d not in (64, 128) or qkv.dtype != torch.bfloat16 or kv.k.dtype != torch.bfloat16:
+        return False
+    return library("fast").call_optional(
+        "bfi_attention_prefill_bf16", _ptr(qkv), c_long(qkv.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(kv.k),
+        _ptr(kv.v), _ptr(kv.block_table), c_int(kv.block_table.stride(0)), _ptr(ctx.cu_seqlens), _ptr(ctx.seq_slot),
+        _ptr(ctx.seq_start), c_int(ctx.n_seqs), c_int(ctx.max_seq_tokens), c_int(n_heads), c_int(kv.n_kv_heads),
+        c_int(d), c_int(kv.window or 0), c_float(scale), _stream())

@@ -25,7 +25,7 @@ def test_skinny_gemm_store(m, n, k):
     ref = P.linear(w.float(), a.float())
     for odt, tol in ((torch.float32, 2e-5), (torch.bfloat16, 1e-2)):
         out = torch.full((m, n), float("nan"), dtype=odt, device=DEV)
-        assert fast().linear_bf16(a.to(DEV), w.to(DEV), out, 0)
+        assert fast().skinny_gemm(a.to(DEV), w.to(DEV), out, 0)
         assert rel_err(out.float(), ref) < tol
 
 
@@ -36,11 +36,11 @@ def test_skinny_gemm_epilogues(m):
     w = (torch.randn(n, k, generator=gen(3)) * 0.05).bfloat16()
     res = torch.randn(m, n, generator=gen(4))
     out = res.clone().to(DEV)
-    assert fast().linear_bf16(a.to(DEV), w.to(DEV), out, 1)
+    assert fast().skinny_gemm(a.to(DEV), w.to(DEV), out, 1)
     assert rel_err(out, res + P.linear(w.float(), a.float())) < 2e-5
     gate, up = w[0::2].float(), w[1::2].float()          # rows interleaved gate/up
     out2 = torch.full((m, n // 2), float("nan"), dtype=torch.bfloat16, device=DEV)
-    assert fast().linear_bf16(a.to(DEV), w.to(DEV), out2, 2)
+    assert fast().skinny_gemm(a.to(DEV), w.to(DEV), out2, 2)
     assert rel_err(out2.float(), P.swiglu(P.linear(gate, a.float()), P.linear(up, a.float()))) < 1e-2
 
 
@@ -48,14 +48,20 @@ def test_skinny_gemm_declines_what_it_cannot_do():
     a = torch.randn(4, 20, device=DEV).bfloat16()
     w = torch.randn(8, 20, device=DEV).bfloat16()
     out = torch.empty(4, 8, dtype=torch.float32, device=DEV)
-    assert not fast().linear_bf16(a, w, out, 0)                       # K not a multiple of 8
+    assert not fast().skinny_gemm(a, w, out, 0)                       # K not a multiple of 8
+    assert not fast().linear_bf16(a, w, out, 0)                       # nor does the tensor-core kernel take it
     a = torch.randn(65, 64, device=DEV).bfloat16()
     w = torch.randn(8, 64, device=DEV).bfloat16()
-    assert not fast().linear_bf16(a, w, torch.empty(65, 8, dtype=torch.float32, device=DEV), 0)   # too many rows
-    # the dispatcher then takes the general kernel and the result is still right
+    assert not fast().skinny_gemm(a, w, torch.empty(65, 8, dtype=torch.float32, device=DEV), 0)   # too many rows
+    # the dispatcher then takes another kernel and the result is still right
     from builderforce_inference_b200.kernels.linear import linear
     out = torch.empty(65, 8, dtype=torch.float32, device=DEV)
     linear(a, w, out)
+    assert rel_err(out, a.float().cpu() @ w.float().cpu().t()) < 2e-5
+    a = torch.randn(70, 20, device=DEV).bfloat16()
+    w = torch.randn(9, 20, device=DEV).bfloat16()
+    out = torch.empty(70, 9, dtype=torch.float32, device=DEV)
+    linear(a, w, out)                                                  # K = 20: only the general kernel takes it
     assert rel_err(out, a.float().cpu() @ w.float().cpu().t()) < 2e-5
 
 
@@ -147,8 +153,136 @@ def test_skinny_gemm_splits_k_between_blocks_and_stays_deterministic(m):
     outs = []
     for _ in range(3):
         out = res.clone().to(DEV)
-        assert fast().linear_bf16(a, w, out, 1)
+        assert fast().skinny_gemm(a, w, out, 1)
         outs.append(out.cpu())
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
     assert rel_err(outs[0], res + P.linear(w.float().cpu(), a.float().cpu())) < 2e-5
     assert int(fast()._split_scratch.counters[a.device].abs().sum()) == 0
+
+
+# ------------------------------------------------------------------ tcgen05 / TMA matrix product
+def tc_check(m, n, k, epi, seed=0):
+    g = gen(seed + m + n)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) * 0.05).bfloat16()
+    ref = P.linear(w.float(), a.float())
+    if epi == 1:
+        res = torch.randn(m, n, generator=g)
+        out = res.clone().to(DEV)
+        ref = res + ref
+    elif epi == 2:
+        out = torch.full((m, n // 2), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ref = P.swiglu(ref[:, 0::2], ref[:, 1::2])
+    else:
+        out = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+    assert fast().gemm_tcgen05(a.to(DEV), w.to(DEV), out, epi)
+    torch.cuda.synchronize()
+    assert int(fast().tc_status(torch.device(DEV)).item()) == 0, "a bounded wait ran out"
+    assert rel_err(out.float(), ref) < (1e-2 if epi == 2 else 3e-5), (m, n, k, epi)
+
+
+@pytest.mark.parametrize("m", [1, 9, 16, 17, 33, 64, 65, 128, 129, 300, 1000])
+@pytest.mark.parametrize("n,k", [(128, 64), (130, 136), (2560, 1024), (72, 200), (640, 2568)])
+def test_gemm_tcgen05_any_size(m, n, k):
+    """Token counts around every tile size, widths that are no multiple of 128 (ragged last tile),
+    K that is no multiple of 64 (zero-filled tail) and small enough to leave splits empty."""
+    tc_check(m, n, k, 0)
+
+
+@pytest.mark.parametrize("m,n,k", [(12, 2560, 4096), (64, 2560, 9728), (40, 6144, 2560), (200, 384, 4096), (2048, 2560, 512)])
+@pytest.mark.parametrize("epi", [0, 1, 2])
+def test_gemm_tcgen05_epilogues_with_and_without_split(m, n, k, epi):
+    """Few row tiles make the blocks of a tile a cluster that splits K; the sum is added in split
+    order out of the blocks' shared memory, so two runs agree to the bit."""
+    tc_check(m, n, k, epi)
+    g = gen(1)
+    a = torch.randn(m, k, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(n, k, generator=g) * 0.05).bfloat16().to(DEV)
+    outs = []
+    for _ in range(2):
+        out = torch.zeros(m, n, dtype=torch.float32, device=DEV)
+        assert fast().gemm_tcgen05(a, w, out, 0)
+        outs.append(out.cpu())
+    assert torch.equal(outs[0], outs[1])
+
+
+def test_gemm_tcgen05_strided_operands_and_refusals():
+    big = torch.randn(50, 4096, generator=gen(2)).bfloat16().to(DEV)
+    a = big[:, 1024:1024 + 512]                                    # row stride 4096, 512 columns
+    w = (torch.randn(300, 512, generator=gen(3)) * 0.05).bfloat16().to(DEV)
+    out_big = torch.zeros(50, 1000, dtype=torch.float32, device=DEV)
+    out = out_big[:, 100:400]
+    assert fast().gemm_tcgen05(a, w, out, 0)
+    assert rel_err(out, a.float().cpu() @ w.float().cpu().t()) < 3e-5
+    assert float(out_big[:, :100].abs().sum()) == 0 and float(out_big[:, 400:].abs().sum()) == 0
+    assert not fast().gemm_tcgen05(big[:, 3:3 + 64], w[:, :64], torch.zeros(50, 300, device=DEV), 0)   # unaligned base
+    assert not fast().gemm_tcgen05(big[:, :20], w[:, :20], torch.zeros(50, 300, device=DEV), 0)        # K % 8 != 0
+
+
+# ------------------------------------------------------------------ tensor-core prompt attention
+class PrefillCtx:
+    def __init__(self, seqs):
+        i32 = lambda xs: torch.tensor(xs, dtype=torch.int32, device=DEV)
+        cu = [0]
+        for _, _, t in seqs:
+            cu.append(cu[-1] + t)
+        self.n_seqs, self.n_tokens = len(seqs), cu[-1]
+        self.max_seq_tokens = max(t for _, _, t in seqs)
+        self.cu_seqlens, self.seq_slot, self.seq_start = i32(cu), i32([s for s, _, _ in seqs]), i32([st for _, st, _ in seqs])
+
+
+@pytest.mark.parametrize("n_q,n_kv,d", [(8, 2, 64), (4, 4, 128), (6, 1, 128), (3, 3, 64)])
+@pytest.mark.parametrize("window", [None, 70])
+def test_attention_prefill(n_q, n_kv, d, window):
+    """Whole prompts, continuations of a cached prefix and single tokens in one launch, lengths around
+    the 16-token warp rows, the 64-token blocks and the 64-key pages; one padding sequence."""
+    seqs = [(2, 0, 33), (0, 0, 1), (3, 95, 1), (1, 31, 34), (-1, 0, 5), (4, 64, 64), (5, 0, 200), (6, 63, 130), (7, 10, 17)]
+    pages = Pages(8, 400, n_kv, d, torch.bfloat16, window=window, seed=d + n_q)
+    g = gen(n_q * 10 + d)
+    scale = 1.0 / math.sqrt(d)
+    qs, refs = [], []
+    for slot, start, t in seqs:
+        n = start + t
+        k = torch.randn(n, n_kv, d, generator=g).bfloat16().float()
+        v = torch.randn(n, n_kv, d, generator=g).bfloat16().float()
+        qq = torch.randn(t, n_q, d, generator=g).bfloat16().float()
+        if slot >= 0:
+            pages.write(slot, 0, k, v)
+        qs.append(qq.reshape(t, n_q * d))
+        refs.append(plain_paged_attention(qq, k, v, start, window, scale).reshape(t, n_q * d))
+    q_all = torch.cat(qs).bfloat16().to(DEV)
+    out = torch.full(q_all.shape, float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert fast().attention_prefill_bf16(PrefillCtx(seqs), q_all, out, pages.view, n_q, scale)
+    got, ref = out.float().cpu(), torch.cat(refs)
+    o = 0
+    for slot, start, t in seqs:
+        if slot < 0:
+            assert torch.isnan(got[o:o + t]).all()
+        else:
+            assert rel_err(got[o:o + t], ref[o:o + t]) < 1e-2, (slot, start, t)
+        o += t
+
+
+def test_attention_prefill_far_key_and_causality():
+    """A dominating key far back must be found by late queries and must not leak to earlier ones."""
+    n_q, n_kv, d, n = 4, 2, 128, 600
+    g = gen(5)
+    scale = 1.0 / math.sqrt(d)
+    q = torch.randn(n, n_q, d, generator=g)
+    q = q / q.norm(dim=-1, keepdim=True)
+    v = torch.randn(n, n_kv, d, generator=g)
+    k = torch.randn(n, n_kv, d, generator=g) * 0.05
+    target = 257
+    k[target, 0] = q[500, 0] * 40.0 * math.sqrt(d)       # query 500, head 0 must find key 257
+    k[target, 1] = q[100, 2] * 40.0 * math.sqrt(d)       # query 100 (head 2) lies before the key: must not see it
+    pages = Pages(1, n, n_kv, d, torch.bfloat16)
+    pages.write(0, 0, k, v)
+    out = torch.empty(n, n_q * d, dtype=torch.bfloat16, device=DEV)
+    assert fast().attention_prefill_bf16(PrefillCtx([(0, 0, n)]), q.reshape(n, -1).bfloat16().to(DEV), out, pages.view,
+                                         n_q, scale)
+    got = out.float().cpu().reshape(n, n_q, d)
+    kq, vq = pages.read(0, n)
+    ref = plain_paged_attention(q.bfloat16().float(), kq, vq, 0, None, scale)
+    assert rel_err(got, ref) < 1e-2
+    assert (got[500, 0] - vq[target, 0]).abs().max() < 0.05
+    assert (got[100, 2] - vq[target, 1]).abs().max() > 0.2

@@ -49,7 +49,7 @@ def test_static_scratch_matches_the_ordinary_entry_point_twice_in_a_row(m):
         a = torch.randn(m, k, generator=g).bfloat16().to(DEV)
         res = torch.randn(m, n, generator=g).to(DEV)
         want = res.clone()
-        assert fast_ops.linear_bf16(a, w, want, 1)
+        assert fast_ops.skinny_gemm(a, w, want, 1)
         got = res.clone()
         assert _static(lib, a, w, got, 1) == 0, lib.bfi_last_error()
         torch.cuda.synchronize()
@@ -60,7 +60,7 @@ def test_static_scratch_matches_the_ordinary_entry_point_twice_in_a_row(m):
     a2 = torch.randn(m, 512, generator=g).bfloat16().to(DEV)
     want = torch.empty(m, 6144, dtype=torch.bfloat16, device=DEV)
     got = torch.empty_like(want)
-    assert fast_ops.linear_bf16(a2, w2, want, 0)
+    assert fast_ops.skinny_gemm(a2, w2, want, 0)
     assert _static(lib, a2, w2, got, 0) == 0
     torch.cuda.synchronize()
     assert rel_err(got.float(), want.float()) < 1e-2

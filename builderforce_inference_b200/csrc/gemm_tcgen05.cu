@@ -349,6 +349,241 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 }
 
 // ------------------------------------------------------------------------------------------
+// Many tokens (prompts): tokens on the lanes.  D[128 tokens, 256 features] per tile, so a thread
+// holds 16 consecutive features of one token after tcgen05.ld and stores them as whole 16-byte
+// words (and SiLU*mul pairs sit in one thread).  The kernel is persistent: each block walks over
+// tiles, and the two halves of tensor memory (2 x 256 columns) alternate as accumulators, so the
+// epilogue of one tile runs while the tensor cores work on the next.
+//   barriers: full/empty per ring stage, tmem_full/tmem_empty per accumulator
+// ------------------------------------------------------------------------------------------
+#define TP_TOKENS 128
+#define TP_FEATS 256
+#define TP_STAGE_BYTES ((TP_TOKENS + TP_FEATS) * TC_BK * 2)      // 48 KB
+#define TP_STAGES 4
+#define TP_SMEM ((size_t)TP_STAGES * TP_STAGE_BYTES + 1024 + 256)
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                            void* __restrict__ C, int c_dtype, long ldc, int M, int N, int K, int tiles_m, int tiles_n,
+                            int epilogue, int vec_ok, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)TP_STAGES * TP_STAGE_BYTES);
+    uint64_t* empty = full + TP_STAGES;
+    uint64_t* tmem_full = empty + TP_STAGES;      // [2]
+    uint64_t* tmem_empty = tmem_full + 2;         // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    int* s_flag = reinterpret_cast<int*>(tmem_slot + 1);
+
+    pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_kb = (K + TC_BK - 1) / TC_BK;
+    const int n_tiles = tiles_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TP_STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&tmem_full[a], 1);
+            mbar_init(&tmem_empty[a], 4);          // one arrival per epilogue warp
+        }
+        s_flag[0] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();
+
+    // tiles in bands of 8 token tiles: blocks that run together share W tiles and A tiles in L2
+    auto tile_coords = [&](int tile, int& tm, int& tn) {
+        const int band = 8;
+        const int per_band = band * tiles_n;
+        const int b = tile / per_band, r = tile - b * per_band;
+        const int rows_here = min(band, tiles_m - b * band);
+        tn = r / rows_here;
+        tm = b * band + (r - tn * rows_here);
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;                                            // k blocks issued so far, over all tiles
+            for (int tile = blockIdx.x; tile < n_tiles && !s_flag[0]; tile += gridDim.x) {
+                int tm, tn;
+                tile_coords(tile, tm, tn);
+                for (int i = 0; i < n_kb; ++i, ++it) {
+                    const int s = it % TP_STAGES;
+                    const uint32_t phase = (it / TP_STAGES) & 1;
+                    if (it >= TP_STAGES && !mbar_wait(&empty[s], phase ^ 1)) {
+                        atomicOr(status, BFI_STATUS_TIMEOUT);
+                        s_flag[0] = 1;
+                        break;
+                    }
+                    unsigned char* stage = smem + (size_t)s * TP_STAGE_BYTES;
+                    mbar_expect_tx(&full[s], TP_STAGE_BYTES);
+                    tma_load_2d(stage, &map_a, i * TC_BK, tm * TP_TOKENS, &full[s]);
+                    tma_load_2d(stage + TP_TOKENS * TC_BK * 2, &map_w, i * TC_BK, tn * TP_FEATS, &full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(TP_TOKENS, TP_FEATS);
+            int it = 0, local = 0;
+            for (int tile = blockIdx.x; tile < n_tiles && !s_flag[0]; tile += gridDim.x, ++local) {
+                const int acc = local & 1;
+                const uint32_t use = (uint32_t)(local >> 1);       // how often this accumulator was used before
+                if (local >= 2 && !mbar_wait(&tmem_empty[acc], (use & 1) ^ 1)) {
+                    atomicOr(status, BFI_STATUS_TIMEOUT);
+                    s_flag[0] = 1;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_addr = tmem_base + (uint32_t)acc * TP_FEATS;
+                bool ok = true;
+                for (int i = 0; i < n_kb; ++i, ++it) {
+                    const int s = it % TP_STAGES;
+                    const uint32_t phase = (it / TP_STAGES) & 1;
+                    if (!mbar_wait(&full[s], phase)) {
+                        atomicOr(status, BFI_STATUS_TIMEOUT);
+                        s_flag[0] = 1;
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t aa = smem_u32(smem + (size_t)s * TP_STAGE_BYTES);
+                    const uint32_t wa = aa + TP_TOKENS * TC_BK * 2;
+#pragma unroll
+                    for (int kk = 0; kk < TC_BK / 16; ++kk)
+                        umma_bf16(d_addr, umma_desc_sw128(aa + kk * 32), umma_desc_sw128(wa + kk * 32), idesc,
+                                  (i > 0 || kk > 0) ? 1u : 0u);
+                    umma_commit(&empty[s]);
+                }
+                umma_commit(&tmem_full[acc]);
+                if (!ok) break;
+            }
+        }
+    } else {
+        const int quad = warp & 3;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
+            const int acc = local & 1;
+            const uint32_t use = (uint32_t)(local >> 1);
+            int tm, tn;
+            tile_coords(tile, tm, tn);
+            if (!mbar_wait(&tmem_full[acc], use & 1)) {
+                if (lane == 0) {
+                    atomicOr(status, BFI_STATUS_TIMEOUT);
+                    s_flag[0] = 1;
+                }
+                break;
+            }
+            tc_fence_after();
+            const int m = tm * TP_TOKENS + quad * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * TP_FEATS;
+#pragma unroll 1
+            for (int c = 0; c < TP_FEATS / 16; ++c) {
+                const int n = tn * TP_FEATS + c * 16;
+                if (n >= N) break;
+                float v[16];
+                tmem_ld16(taddr + c * 16, v);
+                if (m >= M) continue;
+                const bool whole = vec_ok && n + 16 <= N;
+                if (epilogue == EPI_SWIGLU) {
+                    if (whole) {
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            pk[j] = c_dtype == BFI_BF16
+                                        ? ([&] {
+                                              __nv_bfloat162 t2 = __floats2bfloat162_rn(silu_mul_tc(v[4 * j], v[4 * j + 1]),
+                                                                                        silu_mul_tc(v[4 * j + 2], v[4 * j + 3]));
+                                              return *reinterpret_cast<uint32_t*>(&t2);
+                                          })()
+                                        : 0u;
+                        if (c_dtype == BFI_BF16) {
+                            *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(C) + (size_t)m * ldc + (n >> 1)) =
+                                make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                        } else {
+                            float* o = reinterpret_cast<float*>(C) + (size_t)m * ldc + (n >> 1);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) o[j] = silu_mul_tc(v[2 * j], v[2 * j + 1]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; j += 2)
+                            if (n + j + 1 < N)
+                                store_from_f32(C, c_dtype, (size_t)m * ldc + ((n + j) >> 1), silu_mul_tc(v[j], v[j + 1]));
+                    }
+                } else if (epilogue == EPI_ACCUMULATE) {
+                    float* o = reinterpret_cast<float*>(C) + (size_t)m * ldc + n;
+                    if (whole) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            float4 x = *reinterpret_cast<float4*>(o + 4 * j);
+                            x.x += v[4 * j];
+                            x.y += v[4 * j + 1];
+                            x.z += v[4 * j + 2];
+                            x.w += v[4 * j + 3];
+                            *reinterpret_cast<float4*>(o + 4 * j) = x;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (n + j < N) o[j] += v[j];
+                    }
+                } else if (whole && c_dtype == BFI_BF16) {
+                    uint32_t pk[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        __nv_bfloat162 t2 = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                        pk[j] = *reinterpret_cast<uint32_t*>(&t2);
+                    }
+                    uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(C) + (size_t)m * ldc + n);
+                    o[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    o[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                } else if (whole) {
+                    float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(C) + (size_t)m * ldc + n);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) o[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (n + j < N) store_from_f32(C, c_dtype, (size_t)m * ldc + n + j, v[j]);
+                }
+            }
+            // this warp is done with the accumulator: the tensor cores may overwrite it
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (s_flag[0] && warp == 0 && lane == 0) {
+        // a wait ran out: give outstanding TMA writes a bounded time to land
+        for (int s = 0; s < TP_STAGES; ++s) mbar_wait(&full[s], 0), mbar_wait(&full[s], 1);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
 // Host side: tensor maps (cached), planning, launch
 // ------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -490,6 +725,38 @@ static int launch_tc(const TcPlan& p, const CUtensorMap& mw, const CUtensorMap& 
     return bfi_check_launch("gemm_tcgen05");
 }
 
+static int launch_tc_prefill(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype, long ldc, int M,
+                             int N, int K, int epilogue, int* status, cudaStream_t stream) {
+    CUtensorMap ma, mw;
+    int rc = tensor_map(A, M, K, lda, TP_TOKENS, &ma);
+    if (rc) return rc;
+    rc = tensor_map(W, N, K, ldw, TP_FEATS, &mw);
+    if (rc) return rc;
+    static bool configured = false;
+    static int n_sm = 148;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)TP_SMEM);
+        if (e != cudaSuccess)
+            return bfi_fail("gemm_tcgen05: cannot reserve %zu bytes of shared memory: %s", (size_t)TP_SMEM, cudaGetErrorString(e));
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+        configured = true;
+    }
+    const int tiles_m = (M + TP_TOKENS - 1) / TP_TOKENS, tiles_n = (N + TP_FEATS - 1) / TP_FEATS;
+    const long tiles = (long)tiles_m * tiles_n;
+    const int grid = (int)(tiles < n_sm ? tiles : n_sm);
+    // whole 16-byte stores need aligned rows: output row stride and base
+    const int out_cols_shift = epilogue == EPI_SWIGLU ? 1 : 0;
+    (void)out_cols_shift;
+    const int elem = dtype_size(c_dtype);
+    const int vec_ok = ((ldc * elem) % 16 == 0 && ((uintptr_t)C & 15) == 0) ? 1 : 0;
+    bfi_launch(gemm_tcgen05_prefill_kernel, dim3(grid), dim3(TC_THREADS), TP_SMEM, stream, ma, mw, C, c_dtype, ldc, M, N, K,
+               tiles_m, tiles_n, epilogue, vec_ok, status);
+    return bfi_check_launch("gemm_tcgen05_prefill");
+}
+
 // Returns 0 on success, 1 on error, 2 when the shape is not taken (nothing launched).
 // `status` receives BFI_STATUS_TIMEOUT (8) if a bounded wait inside the kernel ran out.
 extern "C" int bfi_gemm_tcgen05_bf16(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype, long ldc,
@@ -503,6 +770,7 @@ extern "C" int bfi_gemm_tcgen05_bf16(const void* A, long lda, const void* W, lon
     if (M == 0) return 0;
     // TMA: 16-byte aligned bases and row strides
     if (K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return 2;
+    if (M >= 128) return launch_tc_prefill(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, status, stream);
     TcPlan p = plan_tc(M, N, K);
     if (p.tiles_m > 65535) return 2;
     CUtensorMap mw, ma;

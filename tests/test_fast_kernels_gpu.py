@@ -286,3 +286,23 @@ def test_attention_prefill_far_key_and_causality():
     assert rel_err(got, ref) < 1e-2
     assert (got[500, 0] - vq[target, 0]).abs().max() < 0.05
     assert (got[100, 2] - vq[target, 1]).abs().max() > 0.2
+
+
+@pytest.mark.parametrize("m", [128, 129, 255, 1000, 2100])
+@pytest.mark.parametrize("n,k,epi", [(256, 64, 0), (130, 136, 0), (2568, 1024, 1), (304, 2560, 2), (6144, 2560, 0), (72, 200, 2)])
+def test_gemm_tcgen05_many_tokens(m, n, k, epi):
+    """128 tokens or more take the persistent kernel (tokens on the lanes, two accumulators in
+    tensor memory); ragged token and feature tiles, K tails, every epilogue."""
+    tc_check(m, n, k, epi, seed=7)
+
+
+def test_gemm_tcgen05_many_tokens_unaligned_output_rows():
+    """An output whose rows are not 16-byte aligned takes the scalar stores and is still right."""
+    m, n, k = 300, 200, 512
+    a = torch.randn(m, k, generator=gen(1)).bfloat16().to(DEV)
+    w = (torch.randn(n, k, generator=gen(2)) * 0.05).bfloat16().to(DEV)
+    big = torch.zeros(m, 333, dtype=torch.bfloat16, device=DEV)
+    out = big[:, 7:207]
+    assert fast().gemm_tcgen05(a, w, out, 0)
+    assert rel_err(out.float(), a.float().cpu() @ w.float().cpu().t()) < 1e-2
+    assert float(big[:, :7].abs().sum()) == 0 and float(big[:, 207:].abs().sum()) == 0

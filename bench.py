@@ -191,8 +191,95 @@ def prefill_run(model, tokens, reps, layers):
     return {"ms": ms, "tok_s": tokens / (ms / 1e3), "flops": flops}
 
 
+KERNEL_SHAPES = {"qkv": (6144, 2560, 0), "o": (2560, 4096, 1), "gateup": (19456, 2560, 2), "down": (2560, 9728, 1),
+                 "head": (151936, 2560, 0)}
+
+
+def kernel_run(a) -> int:
+    """Times ONE kernel on one workload (for profiling under ncu and for the files in profiles/):
+    ``--kernel skinny_gemm|gemm_tcgen05 --shape qkv|o|gateup|down|head --rows M`` or
+    ``--kernel attention_decode|attention_prefill --rows B_or_T --ctx C``.  Weights rotate over
+    enough copies to exceed L2.  Prints one JSON line."""
+    import torch
+    from builderforce_inference_b200.kernels import fast_ops
+    dev = torch.device("cuda:0")
+    reps = a.steps
+    if a.kernel in ("skinny_gemm", "gemm_tcgen05"):
+        n, k, epi = KERNEL_SHAPES[a.shape]
+        m = a.rows
+        copies = max(2, int(400e6 // (n * k * 2)) + 1)
+        ws = [torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+        x = torch.randn(m, k, device=dev, dtype=torch.bfloat16)
+        out = torch.zeros(m, n // 2 if epi == 2 else n, device=dev, dtype=torch.float32 if epi == 1 else torch.bfloat16)
+        fn = fast_ops.skinny_gemm if a.kernel == "skinny_gemm" else fast_ops.gemm_tcgen05
+
+        def one(i):
+            if not fn(x, ws[i % copies], out, epi):
+                raise SystemExit(f"{a.kernel} does not take M={m} N={n} K={k}")
+        bytes_moved, flops = n * k * 2, 2.0 * m * n * k
+        what = {"shape": a.shape, "M": m, "N": n, "K": k, "epilogue": epi}
+    else:
+        from builderforce_inference_b200.cache import KVView
+        c = CONFIG_4B
+        nq, nkv, d = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"]
+        decode = a.kernel == "attention_decode"
+        n_seq = a.rows if decode else 1
+        t_new = 1 if decode else a.rows
+        ctx_len = a.ctx if decode else t_new
+        blocks = (ctx_len + 63) // 64
+        n_pages = n_seq * blocks
+        kp = torch.randn(n_pages, nkv, 64, d, device=dev, dtype=torch.bfloat16)
+        vp = torch.randn(n_pages, nkv, 64, d, device=dev, dtype=torch.bfloat16)
+        table = torch.arange(n_pages, dtype=torch.int32, device=dev).reshape(n_seq, blocks)
+        kv = KVView(kp, vp, table, nkv, d, None)
+        q = torch.randn(n_seq * t_new, (nq + 2 * nkv) * d, device=dev, dtype=torch.bfloat16)
+        out = torch.empty(n_seq * t_new, nq * d, device=dev, dtype=torch.bfloat16)
+
+        class Ctx:
+            pass
+        ctx = Ctx()
+        from builderforce_inference_b200.engine.context import Workspace
+        ctx.workspace = Workspace(dev)
+        ctx.n_seqs, ctx.n_tokens, ctx.max_seq_tokens = n_seq, n_seq * t_new, t_new
+        ctx.seq_slot = torch.arange(n_seq, dtype=torch.int32, device=dev)
+        ctx.seq_start = torch.full((n_seq,), ctx_len - t_new, dtype=torch.int32, device=dev)
+        ctx.cu_seqlens = torch.arange(0, (n_seq + 1) * t_new, t_new, dtype=torch.int32, device=dev)
+        ctx.total_pages = torch.tensor([n_seq * blocks], dtype=torch.int32, device=dev)
+        fn = fast_ops.attention_decode_bf16 if decode else fast_ops.attention_prefill_bf16
+
+        def one(i):
+            if not fn(ctx, q, out, kv, nq, d ** -0.5):
+                raise SystemExit(f"{a.kernel} does not take this shape")
+        bytes_moved = n_seq * ctx_len * 2 * nkv * d * 2
+        flops = 4.0 * nq * d * (n_seq * ctx_len if decode else t_new * (t_new + 1) / 2)
+        what = {"seqs": n_seq, "new_tokens": t_new, "context": ctx_len, "q_heads": nq, "kv_heads": nkv, "head_dim": d}
+    for i in range(3):
+        one(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(reps):
+        one(i)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / reps
+    pk = peaks()
+    print(json.dumps({"kernel": a.kernel, **what, "us": round(us, 2), "launches": reps,
+                      "GB_s": round(bytes_moved / us / 1e3, 1), "TFLOP_s": round(flops / us / 1e6, 1),
+                      "frac_hbm": round(bytes_moved / us / 1e3 / pk["hbm_gbs"], 3),
+                      "frac_bf16": round(flops / us / 1e6 / pk["bf16_tflops"], 3), "peaks": pk["source"],
+                      "note": "eager launches: short kernels include launch gaps"}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", default=None, choices=["skinny_gemm", "gemm_tcgen05", "attention_decode",
+                                                       "attention_prefill"],
+                    help="time one kernel instead of the model (see kernel_run)")
+    ap.add_argument("--shape", default="qkv", choices=sorted(KERNEL_SHAPES))
+    ap.add_argument("--rows", type=int, default=8)
+    ap.add_argument("--ctx", type=int, default=2048)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
@@ -206,6 +293,8 @@ def main() -> int:
                           "the reference is a Rust workspace: no Rust toolchain or network here to build it, "
                           "pip cannot install it, and its CUDA backend runs no kernel for bf16 weights"}))
         return 0
+    if a.kernel is not None:
+        return kernel_run(a)
     if a.gpus != 1:
         print(f"bench.py measures one GPU: this library has no multi-GPU path (asked for --gpus {a.gpus})")
         return 2

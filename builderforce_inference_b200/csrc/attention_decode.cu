@@ -3,24 +3,33 @@
 // once, so the work is split over (sequence, kv head, range of pages): each block streams its
 // pages of 64 keys through a two-stage cp.async ring in shared memory, all query heads of the
 // group share the loaded keys and values (they are the 16 rows of the tensor-core tiles), and
-// partial results (running maximum, sum and unnormalised output, float32) go to a scratch buffer
-// that a second kernel merges in a fixed order.
+// partial results (running maximum, sum and unnormalised output, float32) go to a scratch buffer.
+// They are merged in range order: by the last block of a (sequence, kv head) to finish (a counter,
+// no waiting) when the batch is small, by a second kernel otherwise.
 //
 // Scores, the running maximum and sum, and the output accumulator are float32; exp is
 // ex2.approx on scores pre-multiplied by log2(e).
 #include "attention_tiles.cuh"
 
-// part_o  [seqs, n_q, splits, D]  float32 unnormalised outputs
-// part_ml [seqs, n_q, splits, 2]  float32 (running max in log2 units, running sum)
+// A sequence's pages are cut into at most `max_splits` ranges of equal size (in pages), so every
+// sequence, long or short, spreads over the same number of blocks.
+__device__ __forceinline__ int decode_pages_per_split(int n_pages, int max_splits) {
+    return (n_pages + max_splits - 1) / max_splits;
+}
+
+// part_o  [seqs, n_q, max_splits, D]  float32 unnormalised outputs
+// part_ml [seqs, n_q, max_splits, 2]  float32 (running max in log2 units, running sum)
+// counters [seqs, gridDim.y] int32, zero before the launch and zero again after it
 template <int D>
 __global__ void __launch_bounds__(AD_THREADS)
 attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out, long out_stride,
                         const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                         const int* __restrict__ block_table, int table_stride, const int* __restrict__ seq_slot,
                         const int* __restrict__ seq_start, int n_q, int n_kv, int window, float scale_log2,
-                        int head_chunks, float* __restrict__ part_o, float* __restrict__ part_ml) {
-    pdl_trigger();
+                        int head_chunks, float* __restrict__ part_o, float* __restrict__ part_ml,
+                        int* __restrict__ counters) {
     pdl_wait();
+    pdl_trigger();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* ks[2] = {reinterpret_cast<bf16*>(smem_raw), reinterpret_cast<bf16*>(smem_raw) + 2 * AD_TILE * D};
     bf16* vs[2] = {ks[0] + AD_TILE * D, ks[1] + AD_TILE * D};
@@ -28,7 +37,7 @@ attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
     const int seq = blockIdx.z;
     const int slot = seq_slot[seq];
     if (slot < 0) return;
-    const int n_splits = gridDim.x, split = blockIdx.x;
+    const int max_splits = gridDim.x, split = blockIdx.x;
     const int group = n_q / n_kv;
     const int kvh = blockIdx.y / head_chunks;
     const int hc = blockIdx.y - kvh * head_chunks;
@@ -41,9 +50,11 @@ attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int first_page = lo / AD_TILE, last_page = pos / AD_TILE;
     const int n_pages = last_page - first_page + 1;
-    const int per_split = (n_pages + n_splits - 1) / n_splits;
-    const int p_beg = first_page + split * per_split;
-    const int p_end = min(last_page + 1, p_beg + per_split);
+    const int pages_per_split = decode_pages_per_split(n_pages, max_splits);
+    const int n_splits = (n_pages + pages_per_split - 1) / pages_per_split;    // ranges this sequence has
+    if (split >= n_splits) return;
+    const int p_beg = first_page + split * pages_per_split;
+    const int p_end = min(last_page + 1, p_beg + pages_per_split);
 
     // query fragments: rows g and g+8 are heads head0+g, head0+g+8
     const bf16* qbase = q + (size_t)seq * q_stride;       // one token per sequence: row index = seq
@@ -220,7 +231,7 @@ attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
         if (n_splits == 1) {
             out[(size_t)seq * out_stride + (size_t)head * D + e] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
         } else {
-            const size_t pi = ((size_t)seq * n_q + head) * n_splits + split;
+            const size_t pi = ((size_t)seq * n_q + head) * max_splits + split;
             part_o[pi * D + e] = acc;
             if (e == 0) {
                 part_ml[pi * 2] = m;
@@ -228,37 +239,96 @@ attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
             }
         }
     }
+    if (n_splits == 1 || counters == nullptr) return;     // without counters a second kernel merges
+
+    // ---- the last range of this (sequence, kv head) to arrive merges them all, in range order
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* counter = counters + (size_t)seq * gridDim.y + blockIdx.y;
+        const int ticket = atomicAdd(counter, 1);
+        s_last = ticket == n_splits - 1;
+        if (s_last) *counter = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // weights of the ranges first (one thread per head and range), so that the sums below are
+    // independent loads the memory system can overlap
+    float* fw = reinterpret_cast<float*>(smem_raw);            // [16][max_splits] weights 2^(m_sp - M) / L
+    for (int idx = threadIdx.x; idx < n_heads * 32; idx += AD_THREADS) {
+        const int row = idx >> 5, ln = idx & 31;               // one warp per head
+        const size_t base = ((size_t)seq * n_q + head0 + row) * max_splits;
+        float m = -INFINITY;
+        for (int sp = ln; sp < n_splits; sp += 32) m = fmaxf(m, __ldcg(part_ml + (base + sp) * 2));
+        m = warp_max(m);
+        float l = 0.0f;
+        for (int sp = ln; sp < n_splits; sp += 32) {
+            const float ms = __ldcg(part_ml + (base + sp) * 2);
+            const float f = (ms == -INFINITY) ? 0.0f : fast_exp2(ms - m);
+            fw[row * max_splits + sp] = f;
+            l += __ldcg(part_ml + (base + sp) * 2 + 1) * f;
+        }
+        l = warp_sum(l);
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        __syncwarp();
+        for (int sp = ln; sp < n_splits; sp += 32) fw[row * max_splits + sp] *= inv;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < n_heads * D; idx += AD_THREADS) {
+        const int row = idx / D, e = idx - row * D;
+        const int head = head0 + row;
+        const float* po = part_o + ((size_t)seq * n_q + head) * max_splits * D + e;
+        const float* w = fw + row * max_splits;
+        float acc = 0.0f;
+#pragma unroll 8
+        for (int sp = 0; sp < n_splits; ++sp) acc = fmaf(__ldcg(po + (size_t)sp * D), w[sp], acc);
+        out[(size_t)seq * out_stride + (size_t)head * D + e] = __float2bfloat16_rn(acc);
+    }
 }
 
-// Merges the splits of every (sequence, head) in split order.
+// Merges the ranges of every (sequence, head) in range order: used for larger batches, where a
+// second launch costs less than a fence and a ticket in every block of the first.
 template <int D>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                              const int* __restrict__ seq_slot, bf16* __restrict__ out,
-                                              long out_stride, int n_q, int n_splits) {
-    pdl_trigger();
+                                              const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
+                                              bf16* __restrict__ out, long out_stride, int n_q, int max_splits, int window) {
     pdl_wait();
+    pdl_trigger();
     const int seq = blockIdx.y, head = blockIdx.x;
     if (seq_slot[seq] < 0) return;
-    const size_t base = ((size_t)seq * n_q + head) * n_splits;
+    const int pos = seq_start[seq];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int n_pages = pos / AD_TILE - lo / AD_TILE + 1;
+    const int pps = decode_pages_per_split(n_pages, max_splits);
+    const int n_splits = (n_pages + pps - 1) / pps;
+    if (n_splits == 1) return;                            // the first kernel wrote the output itself
+    const size_t base = ((size_t)seq * n_q + head) * max_splits;
     float m = -INFINITY;
     for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
+    float l = 0.0f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float ms = part_ml[(base + s) * 2];
+        l += part_ml[(base + s) * 2 + 1] * ((ms == -INFINITY) ? 0.0f : fast_exp2(ms - m));
+    }
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
     for (int e = threadIdx.x; e < D; e += blockDim.x) {
-        float l = 0.0f, acc = 0.0f;
+        float acc = 0.0f;
+#pragma unroll 4
         for (int s = 0; s < n_splits; ++s) {
             const float ms = part_ml[(base + s) * 2];
-            const float f = (ms == -INFINITY) ? 0.0f : fast_exp2(ms - m);
-            l += part_ml[(base + s) * 2 + 1] * f;
-            acc += part_o[(base + s) * D + e] * f;
+            acc = fmaf(part_o[(base + s) * D + e], (ms == -INFINITY) ? 0.0f : fast_exp2(ms - m), acc);
         }
-        out[(size_t)seq * out_stride + (size_t)head * D + e] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+        out[(size_t)seq * out_stride + (size_t)head * D + e] = __float2bfloat16_rn(acc * inv);
     }
 }
 
 template <int D>
 static int launch_decode(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
                          const void* v_pages, const int* block_table, int table_stride, const int* seq_slot,
-                         const int* seq_start, int n_seqs, int n_q, int n_kv, int window, float scale, int n_splits,
-                         float* part_o, float* part_ml, cudaStream_t stream) {
+                         const int* seq_start, int n_seqs, int n_q, int n_kv, int window, float scale, int max_splits,
+                         float* part_o, float* part_ml, int* counters, cudaStream_t stream) {
     const int group = n_q / n_kv;
     const int head_chunks = (group + 15) / 16;
     const size_t smem = (size_t)4 * AD_TILE * D * sizeof(bf16);
@@ -270,42 +340,39 @@ static int launch_decode(const void* q, long q_stride, void* out, long out_strid
         if (e != cudaSuccess) return bfi_fail("attention_decode: cannot reserve %zu bytes of shared memory: %s", need,
                                               cudaGetErrorString(e));
     }
-    dim3 grid(n_splits, n_kv * head_chunks, n_seqs);
+    dim3 grid(max_splits, n_kv * head_chunks, n_seqs);
     const float scale_log2 = scale * 1.4426950408889634f;
-    bfi_launch(kernel, dim3(grid), dim3(AD_THREADS), need, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages,
-                                               (const bf16*)v_pages, block_table, table_stride, seq_slot, seq_start,
-                                               n_q, n_kv, window, scale_log2, head_chunks, part_o, part_ml);
+    bfi_launch(kernel, grid, dim3(AD_THREADS), need, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,
+               (const bf16*)k_pages, (const bf16*)v_pages, block_table, table_stride, seq_slot, seq_start, n_q, n_kv, window,
+               scale_log2, head_chunks, part_o, part_ml, counters);
     int rc = bfi_check_launch("attention_decode");
-    if (rc || n_splits == 1) return rc;
-    dim3 mgrid(n_q, n_seqs);
-    bfi_launch(attention_decode_merge_kernel<D>, dim3(mgrid), dim3(D <= 64 ? 64 : 128), 0, stream, part_o, part_ml, seq_slot, (bf16*)out,
-                                                                             out_stride, n_q, n_splits);
+    if (rc || max_splits == 1 || counters != nullptr) return rc;
+    bfi_launch(attention_decode_merge_kernel<D>, dim3(n_q, n_seqs), dim3(D <= 64 ? 64 : 128), 0, stream,
+               (const float*)part_o, (const float*)part_ml, seq_slot, seq_start, (bf16*)out, out_stride, n_q, max_splits,
+               window);
     return bfi_check_launch("attention_decode_merge");
 }
 
-// Floats of scratch the call needs for its partial results: [0] outputs, [1] max/sum pairs.
-extern "C" int bfi_attention_decode_scratch(int n_seqs, int n_q, int head_dim, int n_splits, long* sizes) {
-    sizes[0] = n_splits > 1 ? (long)n_seqs * n_q * n_splits * head_dim : 0;
-    sizes[1] = n_splits > 1 ? (long)n_seqs * n_q * n_splits * 2 : 0;
-    return 0;
-}
-
 // Returns 0 on success, 1 on error, 2 when the shape is not taken (nothing launched).
+// Every sequence's pages are cut into at most `max_splits` ranges.  With max_splits > 1 the caller
+// gives part_o [n_seqs*n_q*max_splits*d], part_ml [n_seqs*n_q*max_splits*2] floats and either
+// counters [n_seqs * n_kv * ceil(group/16)] ints that are zero (the call leaves them zero; the last
+// block of a sequence and kv head merges its ranges) or null (a second kernel merges).
 extern "C" int bfi_attention_decode_bf16(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
                                          const void* v_pages, const int* block_table, int table_stride,
                                          const int* seq_slot, const int* seq_start, int n_seqs, int n_q, int n_kv,
-                                         int d, int window, float scale, int n_splits, float* part_o, float* part_ml,
-                                         cudaStream_t stream) {
+                                         int d, int window, float scale, int max_splits, float* part_o, float* part_ml,
+                                         int* counters, cudaStream_t stream) {
     BFI_REQUIRE(n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_decode: %d query heads do not divide into %d kv heads",
                 n_q, n_kv);
-    BFI_REQUIRE(window >= 0 && n_splits >= 1 && n_splits <= 65535, "attention_decode: bad window or split count");
+    BFI_REQUIRE(window >= 0 && max_splits >= 1 && max_splits <= 65535, "attention_decode: bad window or split count");
     if (n_seqs <= 0) return 0;
     if (d != 64 && d != 128) return 2;
     if (q_stride % 8 != 0 || ((uintptr_t)q & 15) || n_seqs > 65535) return 2;
-    if (n_splits > 1) BFI_REQUIRE(part_o && part_ml, "attention_decode: split runs need the scratch buffers");
+    if (max_splits > 1) BFI_REQUIRE(part_o && part_ml, "attention_decode: split runs need the scratch buffers");
     if (d == 64)
         return launch_decode<64>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride, seq_slot,
-                                 seq_start, n_seqs, n_q, n_kv, window, scale, n_splits, part_o, part_ml, stream);
+                                 seq_start, n_seqs, n_q, n_kv, window, scale, max_splits, part_o, part_ml, counters, stream);
     return launch_decode<128>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride, seq_slot,
-                              seq_start, n_seqs, n_q, n_kv, window, scale, n_splits, part_o, part_ml, stream);
+                              seq_start, n_seqs, n_q, n_kv, window, scale, max_splits, part_o, part_ml, counters, stream);
 }

@@ -162,7 +162,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
     int* s_flag = reinterpret_cast<int*>(tmem_slot + 1);      // [0] error seen, [1] this block reduces the splits
 
-    pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * TC_ROWS;
     const int m0 = blockIdx.y * BT;
@@ -191,6 +190,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();
+    pdl_trigger();
 
     if (warp == 0) {
         // ---------------- TMA producer
@@ -379,7 +379,6 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
     int* s_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
-    pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_kb = (K + TC_BK - 1) / TC_BK;
     const int n_tiles = tiles_m * tiles_n;
@@ -405,6 +404,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();
+    pdl_trigger();
 
     // tiles in bands of 8 token tiles: blocks that run together share W tiles and A tiles in L2
     auto tile_coords = [&](int tile, int& tm, int& tn) {

@@ -127,7 +127,6 @@ __global__ void skinny_gemm_kernel(const bf16* __restrict__ A, long lda, const b
             xa[u][n] = (ok && arow_ok[n]) ? ldg_plain(arow[n] + kk) : zero;         \
     }
 
-    pdl_trigger();
     SKINNY_LOAD(kbeg)
     {
         const int kpre = kbeg + 32 * U;                     // multiple of 32 elements = 64 bytes
@@ -142,6 +141,7 @@ __global__ void skinny_gemm_kernel(const bf16* __restrict__ A, long lda, const b
         }
     }
     pdl_wait();
+    pdl_trigger();       // only now: at most one later kernel sits waiting on the SMs
     for (int k0 = kbeg; k0 < kend; k0 += 32 * U) {
         if (k0 != kbeg) {
             SKINNY_LOAD(k0)

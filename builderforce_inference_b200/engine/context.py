@@ -58,6 +58,7 @@ class StepContext:
     cu_seqlens: torch.Tensor      # [n_seqs + 1] first row of each sequence in the packed tokens
     seq_slot: torch.Tensor        # [n_seqs] slot, -1 for padding
     seq_start: torch.Tensor       # [n_seqs] tokens the sequence held before this step
+    total_pages: torch.Tensor     # [1] cache pages (64 positions) the sequences hold after this step, summed
     status: torch.Tensor          # [1] int32, bits set by device-side checks
     # host copies (None while a captured graph is replayed)
     host_seq_slot: Optional[List[int]] = None
@@ -96,6 +97,7 @@ def build_context(seqs, act_dtype: torch.dtype, workspace: Workspace, device,
         n_tokens=len(ids), n_seqs=len(seqs), max_seq_tokens=max(len(t) for _, _, t in seqs),
         act_dtype=act_dtype, workspace=workspace, token_ids=i32(ids), token_pos=i32(pos),
         token_slot=i32(slot_of), cu_seqlens=i32(cu), seq_slot=i32([s for s, _, _ in seqs]),
-        seq_start=i32([st for _, st, _ in seqs]), status=status,
+        seq_start=i32([st for _, st, _ in seqs]),
+        total_pages=i32([sum((st + len(t) + 63) // 64 for _, st, t in seqs)]), status=status,
         host_seq_slot=[s for s, _, _ in seqs], host_seq_start=[st for _, st, _ in seqs],
         host_seq_tokens=[len(t) for _, _, t in seqs])

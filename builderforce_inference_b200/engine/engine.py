@@ -295,7 +295,7 @@ class Engine:
             x = self.decoder.embed(ctx)
             self.decoder.run_layers(ctx, x, self.cache)
             if rows:
-                row_idx = self._meta_slices(meta, n_tok, n_seq, len(rows))[6]
+                row_idx = self._meta_slices(meta, n_tok, n_seq, len(rows))[7]
                 contiguous = dest == list(range(dest[0], dest[0] + len(dest)))
                 if contiguous:
                     self.decoder.logits(ctx, x, row_idx, out[dest[0]:dest[0] + len(dest)])
@@ -313,10 +313,10 @@ class Engine:
 
     # ---- the packed index arrays of a step -------------------------------------------
     # layout of `meta` (int32): token_ids[T] token_pos[T] token_slot[T] cu_seqlens[B+1] seq_slot[B]
-    #                           seq_start[B] want_rows[W]
+    #                           seq_start[B] total_pages[1] want_rows[W]
     @staticmethod
     def _meta_len(n_tok: int, n_seq: int, n_want: int) -> int:
-        return 3 * n_tok + (n_seq + 1) + 2 * n_seq + n_want
+        return 3 * n_tok + (n_seq + 1) + 2 * n_seq + 1 + n_want
 
     def _meta_buffer(self, n_tok: int, n_seq: int, n_want: int) -> torch.Tensor:
         n = self._meta_len(n_tok, n_seq, n_want)
@@ -326,7 +326,7 @@ class Engine:
     def _meta_slices(meta, n_tok, n_seq, n_want):
         o = 0
         out = []
-        for n in (n_tok, n_tok, n_tok, n_seq + 1, n_seq, n_seq, n_want):
+        for n in (n_tok, n_tok, n_tok, n_seq + 1, n_seq, n_seq, 1, n_want):
             out.append(meta[o:o + n])
             o += n
         return out
@@ -342,7 +342,11 @@ class Engine:
         last = cu[-1]
         host = (list(tok) + [0] * pad_t + list(pos) + [0] * pad_t + list(slot_of) + [-1] * pad_t
                 + list(cu) + [last] * pad_s + list(seq_slots) + [-1] * pad_s
-                + list(seq_starts) + [0] * pad_s + list(want_rows))
+                + list(seq_starts) + [0] * pad_s
+                # pages the sequences hold after this step, summed: kernels size their work split by it
+                + [sum((int(st) + (int(cu[i + 1]) - int(cu[i])) + PAGE_TOKENS - 1) // PAGE_TOKENS
+                       for i, st in enumerate(seq_starts))]
+                + list(want_rows))
         n = len(host)
         pinned = self._pinned.get(n)
         if pinned is None:
@@ -356,11 +360,11 @@ class Engine:
         self.last_h2d_bytes = 4 * n
 
     def _context_from_meta(self, meta, n_tok, n_seq, max_seq_tokens, host) -> StepContext:
-        ids, pos, slot_of, cu, seq_slot, seq_start, _ = self._meta_slices(meta, n_tok, n_seq, 0)
+        ids, pos, slot_of, cu, seq_slot, seq_start, pages, _ = self._meta_slices(meta, n_tok, n_seq, 0)
         ctx = StepContext(
             n_tokens=n_tok, n_seqs=n_seq, max_seq_tokens=max_seq_tokens, act_dtype=self.dtype,
             workspace=self.workspace, token_ids=ids, token_pos=pos, token_slot=slot_of, cu_seqlens=cu,
-            seq_slot=seq_slot, seq_start=seq_start, status=self.status)
+            seq_slot=seq_slot, seq_start=seq_start, total_pages=pages, status=self.status)
         if host is not None:
             ctx.host_seq_slot, ctx.host_seq_start, ctx.host_seq_tokens = host
         return ctx

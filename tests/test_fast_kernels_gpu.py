@@ -74,6 +74,7 @@ class Ctx:
         self.n_seqs = self.n_tokens = len(slots)
         self.max_seq_tokens = 1
         self.seq_slot, self.seq_start = i32(slots), i32(starts)
+        self.total_pages = i32([sum(s // 64 + 1 for s, sl in zip(starts, slots) if sl >= 0)])
         self.workspace = Workspace(torch.device(DEV))
 
 
@@ -99,10 +100,17 @@ def test_attention_decode(n_q, n_kv, d, window, monkeypatch):
     q_all = torch.cat(qs).bfloat16().to(DEV)
     ref = torch.cat(refs)
     for forced in (None, 1, 2, 5, 12):
+        ctx = Ctx(slots, starts)
         if forced is not None:
             monkeypatch.setattr(fast(), "decode_splits", lambda *a, f=forced: f)
+        for fused in (0, 1000):                          # merge by a second kernel, or by the last block
+            monkeypatch.setattr(fast(), "FUSED_MERGE_MAX_GROUPS", fused)
+            out = torch.full((len(starts), n_q * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+            assert fast().attention_decode_bf16(ctx, q_all, out, pages.view, n_q, scale)
+            assert rel_err(out.float().cpu()[[i for i in range(len(starts)) if i != 3]],
+                           ref[[i for i in range(len(starts)) if i != 3]]) < 1e-2, (forced, fused)
         out = torch.full((len(starts), n_q * d), float("nan"), dtype=torch.bfloat16, device=DEV)
-        assert fast().attention_decode_bf16(Ctx(slots, starts), q_all, out, pages.view, n_q, scale)
+        assert fast().attention_decode_bf16(ctx, q_all, out, pages.view, n_q, scale)
         got = out.float().cpu()
         assert torch.isnan(got[3]).all()
         keep = [i for i in range(len(starts)) if i != 3]

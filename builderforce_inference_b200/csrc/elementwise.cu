@@ -300,6 +300,91 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, long token_stride
     }
 }
 
+// The same for bfloat16 heads of 64 or 128 values with the rotation over the whole head: a lane
+// owns 4 consecutive values (8-byte accesses) and its rotation partner sits half a head away in
+// lane ^ (LANES/2), so nothing goes through shared memory.  LANES = head_dim / 4 lanes per head;
+// a warp handles 32 / LANES heads.
+template <int D>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_cache_vec_kernel(bf16* __restrict__ qkv, long token_stride, int n_tokens, int n_q, int n_kv,
+                              const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w, int norm_dtype,
+                              float eps, const float2* __restrict__ rope_table, int table_positions,
+                              const int* __restrict__ token_pos, const int* __restrict__ token_slot,
+                              bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, const int* __restrict__ block_table,
+                              int table_stride, int flags, int* status) {
+    pdl_wait();
+    pdl_trigger();
+    constexpr int LANES = D / 4;
+    constexpr int PER_WARP = 32 / LANES;
+    const int lane = threadIdx.x & 31, sub = lane % LANES;
+    const int heads = n_q + 2 * n_kv;
+    const long item = ((long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * PER_WARP + lane / LANES;
+    const bool live = item < (long)n_tokens * heads;
+    const int t = live ? (int)(item / heads) : 0;
+    const int hh = live ? (int)(item - (long)t * heads) : 0;
+    const int slot = live ? token_slot[t] : -1;
+    const bool work = live && slot >= 0;
+    const int pos = work ? token_pos[t] : 0;
+    const int kind = hh < n_q ? 0 : (hh < n_q + n_kv ? 1 : 2);
+    bf16* src = qkv + (size_t)t * token_stride + (size_t)hh * D + sub * 4;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (work) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(src);
+        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+        v[0] = __low2float(lo); v[1] = __high2float(lo); v[2] = __low2float(hi); v[3] = __high2float(hi);
+    }
+    const void* nw = kind == 0 ? q_norm_w : (kind == 1 ? k_norm_w : nullptr);
+    float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+#pragma unroll
+    for (int o = LANES / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (nw != nullptr) {
+        const float scale = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = v[j] * scale * load_as_f32(nw, norm_dtype, sub * 4 + j);
+    }
+    const bool rotate = kind != 2 && rope_table != nullptr;
+    bool bad_pos = false;
+    float out4[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[j], LANES / 2);
+        out4[j] = v[j];
+        if (rotate && work) {
+            if (pos < 0 || pos >= table_positions) {
+                bad_pos = true;
+            } else {
+                const bool first = sub < LANES / 2;
+                const int pair = (sub % (LANES / 2)) * 4 + j;
+                const float2 c = rope_table[(size_t)pos * (D / 2) + pair];
+                out4[j] = first ? v[j] * c.x - other * c.y : other * c.y + v[j] * c.x;
+            }
+        }
+    }
+    if (!work) return;
+    if (bad_pos) {
+        if (sub == 0 && status) atomicOr(status, BFI_STATUS_BAD_POSITION);
+        return;
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(out4[0], out4[1]), hi = __floats2bfloat162_rn(out4[2], out4[3]);
+    uint2 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<uint32_t*>(&hi);
+    const bool in_place = kind == 0 || (kind == 1 && (flags & 2));
+    if (in_place && (nw != nullptr || rotate)) *reinterpret_cast<uint2*>(src) = packed;
+    if (kind != 0 && (flags & 1)) {
+        const int page = block_table[(size_t)slot * table_stride + pos / BFI_PAGE_TOKENS];
+        if (page < 0) {
+            if (sub == 0 && status) atomicOr(status, BFI_STATUS_NO_PAGE);
+        } else {
+            bf16* pages = kind == 1 ? k_pages : v_pages;
+            const int h = kind == 1 ? hh - n_q : hh - n_q - n_kv;
+            bf16* dst = pages + (((size_t)page * n_kv + h) * BFI_PAGE_TOKENS + (pos % BFI_PAGE_TOKENS)) * D + sub * 4;
+            *reinterpret_cast<uint2*>(dst) = packed;
+        }
+    }
+}
+
 extern "C" int bfi_qk_norm_rope_cache(void* qkv, int dtype, long token_stride, int n_tokens, int n_q, int n_kv,
                                       int d, const void* q_norm_w, const void* k_norm_w, int norm_dtype, float eps,
                                       const void* rope_table, int rot_dim, int table_positions,
@@ -321,6 +406,23 @@ extern "C" int bfi_qk_norm_rope_cache(void* qkv, int dtype, long token_stride, i
         BFI_REQUIRE(k_pages && v_pages && block_table && table_stride > 0, "qk_norm_rope_cache: cache write without a cache");
     if (n_tokens == 0) return 0;
     const long items = (long)n_tokens * (n_q + 2 * n_kv);
+    // bfloat16 heads of 64 or 128 rotated over the whole head (or not at all): the vector kernel
+    const bool vec = dtype == BFI_BF16 && (d == 64 || d == 128) && (rope_table == nullptr || rot_dim == d) &&
+                     token_stride % 4 == 0 && ((uintptr_t)qkv & 7) == 0;
+    if (vec) {
+        const int per_warp = 32 / (d / 4);
+        const long warps = (items + per_warp - 1) / per_warp;
+        const int vblocks = (int)((warps + 3) / 4);
+        if (d == 128)
+            bfi_launch(qk_norm_rope_cache_vec_kernel<128>, dim3(vblocks), dim3(128), 0, stream, (bf16*)qkv, token_stride,
+                       n_tokens, n_q, n_kv, q_norm_w, k_norm_w, norm_dtype, eps, (const float2*)rope_table, table_positions,
+                       token_pos, token_slot, (bf16*)k_pages, (bf16*)v_pages, block_table, table_stride, flags, status);
+        else
+            bfi_launch(qk_norm_rope_cache_vec_kernel<64>, dim3(vblocks), dim3(128), 0, stream, (bf16*)qkv, token_stride,
+                       n_tokens, n_q, n_kv, q_norm_w, k_norm_w, norm_dtype, eps, (const float2*)rope_table, table_positions,
+                       token_pos, token_slot, (bf16*)k_pages, (bf16*)v_pages, block_table, table_stride, flags, status);
+        return bfi_check_launch("qk_norm_rope_cache_vec");
+    }
     const int blocks = (int)((items + QKR_WARPS - 1) / QKR_WARPS);
     if (dtype == BFI_F32)
         bfi_launch(qk_norm_rope_cache_kernel<float>, dim3(blocks), dim3(QKR_WARPS * 32), 0, stream, 

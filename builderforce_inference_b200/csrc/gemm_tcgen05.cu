@@ -122,16 +122,9 @@ __host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-__device__ __forceinline__ float silu_mul_tc(float g, float u) {
-    float s;
-    if (g >= 0.0f) {
-        s = 1.0f / (1.0f + __expf(-g));
-    } else {
-        const float z = __expf(g);
-        s = z / (1.0f + z);
-    }
-    return g * s * u;
-}
+// SiLU(g) * u for the bfloat16 path: g / (1 + e^-g) with the fast exponential and division
+// (e^-g overflowing to infinity for very negative g gives -0, as it should).
+__device__ __forceinline__ float silu_mul_tc(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
 template <int BT>
 struct TcConfig {

@@ -284,7 +284,7 @@ def test_attention_never_reads_past_a_sequence_or_a_padding_row():
 
 # ------------------------------------------------------------------ q/k norm + rotation + cache write
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("n_q,n_kv,d,theta", [(4, 2, 16, 1e4), (6, 3, 48, 1e6), (2, 1, 128, 5e5), (3, 3, 80, 1e4)])
+@pytest.mark.parametrize("n_q,n_kv,d,theta", [(4, 2, 16, 1e4), (6, 3, 48, 1e6), (2, 1, 128, 5e5), (3, 3, 80, 1e4), (5, 5, 64, 1e4), (8, 2, 128, 1e6)])
 def test_qk_norm_rope_cache(dt, n_q, n_kv, d, theta):
     from builderforce_inference_b200.parts.rotary import rotary_table
     g = gen(d)

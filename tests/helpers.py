@@ -48,7 +48,13 @@ TINY_F = _cfg(num_hidden_layers=2, hidden_size=96, num_attention_heads=4, num_ke
               intermediate_size=160, vocab_size=333, rope_theta=1000000.0, rms_norm_eps=1e-6,
               tie_word_embeddings=False, max_position_embeddings=1024)
 
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F}
+# the layer sizes of the benchmark model (Qwen3-4B shape) with two layers and a small vocabulary:
+# the kernels at the sizes they are tuned for
+WIDE = _cfg(num_hidden_layers=2, hidden_size=2560, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+            intermediate_size=9728, vocab_size=4099, rope_theta=1000000.0, rms_norm_eps=1e-6,
+            tie_word_embeddings=True, max_position_embeddings=4096)
+
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F, "WIDE": WIDE}
 
 F32_TOL = 1e-4     # max |got - ref| / max |ref|, float32 run against the plain implementation
 BF16_TOL = 2e-2    # bfloat16 run against the plain implementation on the same (bfloat16) weights

@@ -285,3 +285,36 @@ def test_a_32bit_checkpoint_runs_in_a_bfloat16_engine():
     s = eng.acquire()
     got = eng.step([S(s, p, list(range(40)))]).cpu()
     assert rel_err(got, plain_logits(folder, p)) < tol("bfloat16")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_benchmark_layer_sizes_against_plain(dtype):
+    """Two layers at the Qwen3-4B sizes: a prompt whole (300 tokens: the many-token kernels), its
+    last 12 tokens one by one (the few-row kernels), and an unequal batch of 40 (the kernels in
+    between), all against the plain implementation."""
+    name = "WIDE"
+    folder = model_folder(name, store_dtype(dtype))
+    eng = load(name, dtype, max_tokens=64 * 64)
+    prompts = random_prompts(CONFIGS[name]["vocab_size"], [300, 130, 77], seed=41)
+    refs = [plain_logits(folder, p) for p in prompts]
+    s = eng.acquire()
+    got = eng.step([S(s, prompts[0], list(range(300)))]).cpu()
+    bad = first_bad_row(got, refs[0], dtype)
+    assert bad is None, f"whole prompt: first wrong position {bad}, rel err {rel_err(got, refs[0]):.3e}"
+    eng.release(s)
+    s = eng.acquire()
+    rows = [eng.step([S(s, prompts[0][:288], [287])]).cpu().clone()]
+    for t in range(288, 300):
+        rows.append(eng.step([S(s, [prompts[0][t]], [0])]).cpu().clone())
+    check(torch.cat(rows), refs[0][287:], dtype, "last tokens one by one")
+    eng.release(s)
+    # 40 sequences decode together: 3 real requests and copies of the third at other phases
+    slots = [eng.acquire() for _ in range(40)]
+    pre = [290, 120, 70] + [10 + i for i in range(37)]
+    src = [0, 1, 2] + [2] * 37
+    eng.step([S(sl, prompts[i][:k], []) for sl, i, k in zip(slots, src, pre)])
+    for step in range(5):
+        lg = eng.step([S(sl, [prompts[i][k + step]], [0]) for sl, i, k in zip(slots, src, pre)]).cpu()
+        for j in (0, 1, 2, 3, 20, 39):
+            e = rel_err(lg[j:j + 1], refs[src[j]][pre[j] + step:pre[j] + step + 1])
+            assert e < tol(dtype), f"batch of 40, row {j}, step {step}: rel err {e:.3e}"

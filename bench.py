@@ -228,10 +228,12 @@ def kernel_run(a) -> int:
         ctx_len = a.ctx if decode else t_new
         blocks = (ctx_len + 63) // 64
         n_pages = n_seq * blocks
-        kp = torch.randn(n_pages, nkv, 64, d, device=dev, dtype=torch.bfloat16)
-        vp = torch.randn(n_pages, nkv, 64, d, device=dev, dtype=torch.bfloat16)
         table = torch.arange(n_pages, dtype=torch.int32, device=dev).reshape(n_seq, blocks)
-        kv = KVView(kp, vp, table, nkv, d, None)
+        cache_bytes = n_pages * nkv * 64 * d * 2 * 2
+        copies = max(2, int(400e6 // cache_bytes) + 1) if decode else 1
+        kvs = [KVView(torch.randn(n_pages, nkv, 64, d, device=dev, dtype=torch.bfloat16),
+                      torch.randn(n_pages, nkv, 64, d, device=dev, dtype=torch.bfloat16), table, nkv, d, None)
+               for _ in range(copies)]
         q = torch.randn(n_seq * t_new, (nq + 2 * nkv) * d, device=dev, dtype=torch.bfloat16)
         out = torch.empty(n_seq * t_new, nq * d, device=dev, dtype=torch.bfloat16)
 
@@ -246,9 +248,8 @@ def kernel_run(a) -> int:
         ctx.cu_seqlens = torch.arange(0, (n_seq + 1) * t_new, t_new, dtype=torch.int32, device=dev)
         ctx.total_pages = torch.tensor([n_seq * blocks], dtype=torch.int32, device=dev)
         fn = fast_ops.attention_decode_bf16 if decode else fast_ops.attention_prefill_bf16
-
         def one(i):
-            if not fn(ctx, q, out, kv, nq, d ** -0.5):
+            if not fn(ctx, q, out, kvs[i % copies], nq, d ** -0.5):
                 raise SystemExit(f"{a.kernel} does not take this shape")
         bytes_moved = n_seq * ctx_len * 2 * nkv * d * 2
         flops = 4.0 * nq * d * (n_seq * ctx_len if decode else t_new * (t_new + 1) / 2)
@@ -257,9 +258,14 @@ def kernel_run(a) -> int:
         one(i)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    graph = torch.cuda.CUDAGraph()          # one graph of all launches: no host gaps between short kernels
+    with torch.cuda.graph(graph):
+        for i in range(reps):
+            one(i)
+    graph.replay()
+    torch.cuda.synchronize()
     e0.record()
-    for i in range(reps):
-        one(i)
+    graph.replay()
     e1.record()
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / reps
@@ -268,7 +274,7 @@ def kernel_run(a) -> int:
                       "GB_s": round(bytes_moved / us / 1e3, 1), "TFLOP_s": round(flops / us / 1e6, 1),
                       "frac_hbm": round(bytes_moved / us / 1e3 / pk["hbm_gbs"], 3),
                       "frac_bf16": round(flops / us / 1e6 / pk["bf16_tflops"], 3), "peaks": pk["source"],
-                      "note": "eager launches: short kernels include launch gaps"}))
+                      "note": "launches replayed from one CUDA graph, operands rotating over more than L2"}))
     return 0
 
 

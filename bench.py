@@ -198,7 +198,7 @@ KERNEL_SHAPES = {"qkv": (6144, 2560, 0), "o": (2560, 4096, 1), "gateup": (19456,
 def kernel_run(a) -> int:
     """Times ONE kernel on one workload (for profiling under ncu and for the files in profiles/):
     ``--kernel skinny_gemm|gemm_tcgen05 --shape qkv|o|gateup|down|head --rows M`` or
-    ``--kernel attention_decode|attention_prefill --rows B_or_T --ctx C``.  Weights rotate over
+    ``--kernel attention_decode|attention_prefill|attention_prefill_tcgen05 --rows B_or_T --ctx C``.  Weights rotate over
     enough copies to exceed L2.  Prints one JSON line."""
     import torch
     from builderforce_inference_b200.kernels import fast_ops
@@ -247,7 +247,8 @@ def kernel_run(a) -> int:
         ctx.seq_start = torch.full((n_seq,), ctx_len - t_new, dtype=torch.int32, device=dev)
         ctx.cu_seqlens = torch.arange(0, (n_seq + 1) * t_new, t_new, dtype=torch.int32, device=dev)
         ctx.total_pages = torch.tensor([n_seq * blocks], dtype=torch.int32, device=dev)
-        fn = fast_ops.attention_decode_bf16 if decode else fast_ops.attention_prefill_bf16
+        fn = {"attention_decode": fast_ops.attention_decode_bf16, "attention_prefill": fast_ops.attention_prefill_bf16,
+              "attention_prefill_tcgen05": fast_ops.attention_prefill_tcgen05_bf16}[a.kernel]
         def one(i):
             if not fn(ctx, q, out, kvs[i % copies], nq, d ** -0.5):
                 raise SystemExit(f"{a.kernel} does not take this shape")
@@ -281,7 +282,7 @@ def kernel_run(a) -> int:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default=None, choices=["skinny_gemm", "gemm_tcgen05", "attention_decode",
-                                                       "attention_prefill"],
+                                                       "attention_prefill", "attention_prefill_tcgen05"],
                     help="time one kernel instead of the model (see kernel_run)")
     ap.add_argument("--shape", default="qkv", choices=sorted(KERNEL_SHAPES))
     ap.add_argument("--rows", type=int, default=8)

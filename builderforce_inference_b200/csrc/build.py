@@ -25,7 +25,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 # streaming weights and the cache at memory speed.
 LIBRARIES: Dict[str, List[str]] = {
     "core": ["errors.cu", "elementwise.cu", "gemm_simt.cu", "attention_paged.cu", "sampling.cu"],
-    "fast": ["errors.cu", "skinny_gemm.cu", "attention_decode.cu", "attention_prefill.cu", "gemm_tcgen05.cu"],
+    "fast": ["errors.cu", "skinny_gemm.cu", "attention_decode.cu", "attention_prefill.cu", "gemm_tcgen05.cu",
+             "attention_prefill_tcgen05.cu"],
 }
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]

@@ -19,108 +19,18 @@
 //
 // Every wait on an mbarrier is bounded: a wait that runs out records BFI_STATUS_TIMEOUT in the
 // status word, and the block drains its copies, frees its tensor memory and returns.
-#include <cuda.h>
-
 #include <mutex>
 #include <unordered_map>
 
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 #define EPI_STORE 0
 #define EPI_ACCUMULATE 1
 #define EPI_SWIGLU 2
 
-#define BFI_STATUS_TIMEOUT 8
-
 #define TC_ROWS 128           // W rows per tile (UMMA M)
 #define TC_BK 64              // k elements per stage: one 128-byte swizzle row
 #define TC_THREADS 192
-#define TC_SPIN_LIMIT (1u << 22)
-
-// ------------------------------------------------------------------------------------------
-// PTX wrappers
-// ------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
-        : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols));
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols));
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
-// groups of 8 rows 1024 bytes apart (SBO), version 1, layout type 2.  `addr` may point 32, 64 or
-// 96 bytes into a row to select a 16-element k slice.
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFF) >> 4);          // start address, bits [0,14)
-    d |= (uint64_t)1 << 16;                          // leading byte offset (unused with swizzle), bits [16,30)
-    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset, bits [32,46)
-    d |= (uint64_t)1 << 46;                          // descriptor version for sm_100
-    d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
-    return d;
-}
-// Instruction descriptor, kind::f16: D float32, A and B bfloat16, both K-major, M x N.
-__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
 
 // SiLU(g) * u for the bfloat16 path: g / (1 + e^-g) with the fast exponential and division
 // (e^-g overflowing to infinity for very negative g gives -0, as it should).
@@ -355,9 +265,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #define TP_STAGES 4
 #define TP_SMEM ((size_t)TP_STAGES * TP_STAGE_BYTES + 1024 + 256)
 
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
@@ -617,8 +524,7 @@ struct MapKeyHash {
 static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
 static std::mutex g_maps_mutex;
 
-// A [rows, cols] bfloat16 matrix with row stride ld (elements), read in boxes of box_rows x 64.
-static int tensor_map(const void* ptr, long rows, long cols, long ld, int box_rows, CUtensorMap* out) {
+int bfi_tensor_map_bf16(const void* ptr, long rows, long cols, long ld, int box_rows, CUtensorMap* out) {
     MapKey key{ptr, rows, cols, ld, box_rows};
     std::lock_guard<std::mutex> lock(g_maps_mutex);
     auto it = g_maps.find(key);
@@ -721,9 +627,9 @@ static int launch_tc(const TcPlan& p, const CUtensorMap& mw, const CUtensorMap& 
 static int launch_tc_prefill(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype, long ldc, int M,
                              int N, int K, int epilogue, int* status, cudaStream_t stream) {
     CUtensorMap ma, mw;
-    int rc = tensor_map(A, M, K, lda, TP_TOKENS, &ma);
+    int rc = bfi_tensor_map_bf16(A, M, K, lda, TP_TOKENS, &ma);
     if (rc) return rc;
-    rc = tensor_map(W, N, K, ldw, TP_FEATS, &mw);
+    rc = bfi_tensor_map_bf16(W, N, K, ldw, TP_FEATS, &mw);
     if (rc) return rc;
     static bool configured = false;
     static int n_sm = 148;
@@ -767,9 +673,9 @@ extern "C" int bfi_gemm_tcgen05_bf16(const void* A, long lda, const void* W, lon
     TcPlan p = plan_tc(M, N, K);
     if (p.tiles_m > 65535) return 2;
     CUtensorMap mw, ma;
-    int rc = tensor_map(W, N, K, ldw, TC_ROWS, &mw);
+    int rc = bfi_tensor_map_bf16(W, N, K, ldw, TC_ROWS, &mw);
     if (rc) return rc;
-    rc = tensor_map(A, M, K, lda, p.bt, &ma);
+    rc = bfi_tensor_map_bf16(A, M, K, lda, p.bt, &ma);
     if (rc) return rc;
     switch (p.bt) {
         case 16: return launch_tc<16>(p, mw, ma, C, c_dtype, ldc, M, N, K, epilogue, status, stream);

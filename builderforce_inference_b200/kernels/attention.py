@@ -11,4 +11,7 @@ def attend(ctx, qkv, out, kv, n_heads: int, scale: float) -> bool:
     from . import fast_ops
     if ctx.max_seq_tokens == 1 and ctx.n_tokens == ctx.n_seqs:
         return fast_ops.attention_decode_bf16(ctx, qkv, out, kv, n_heads, scale)
+    if ctx.max_seq_tokens >= fast_ops.TCGEN05_ATTENTION_MIN_TOKENS and \
+            fast_ops.attention_prefill_tcgen05_bf16(ctx, qkv, out, kv, n_heads, scale):
+        return True
     return fast_ops.attention_prefill_bf16(ctx, qkv, out, kv, n_heads, scale)

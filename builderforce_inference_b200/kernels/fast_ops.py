@@ -171,3 +171,22 @@ def attention_prefill_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_head
         _ptr(kv.v), _ptr(kv.block_table), c_int(kv.block_table.stride(0)), _ptr(ctx.cu_seqlens), _ptr(ctx.seq_slot),
         _ptr(ctx.seq_start), c_int(ctx.n_seqs), c_int(ctx.max_seq_tokens), c_int(n_heads), c_int(kv.n_kv_heads),
         c_int(d), c_int(kv.window or 0), c_float(scale), _stream())
+
+
+TCGEN05_ATTENTION_MIN_TOKENS = 128     # shorter steps: the mma.sync kernel with 64-token tiles
+
+
+def attention_prefill_tcgen05_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float) -> bool:
+    """tcgen05 / TMA attention for steps with long runs of new tokens: 128 tokens of one head per
+    block, scores and output in tensor memory.  A wait that ran out shows in ``tc_status``."""
+    d = kv.head_dim
+    if d not in (64, 128) or qkv.dtype != torch.bfloat16 or kv.k.dtype != torch.bfloat16:
+        return False
+    if not kv.k.is_contiguous() or not kv.v.is_contiguous():
+        return False
+    return library("fast").call_optional(
+        "bfi_attention_prefill_tcgen05_bf16", _ptr(qkv), c_long(qkv.stride(0)), _ptr(out), c_long(out.stride(0)),
+        _ptr(kv.k), _ptr(kv.v), c_long(kv.k.shape[0]), _ptr(kv.block_table), c_int(kv.block_table.stride(0)),
+        _ptr(ctx.cu_seqlens), _ptr(ctx.seq_slot), _ptr(ctx.seq_start), c_int(ctx.n_seqs), c_long(qkv.shape[0]),
+        c_int(ctx.max_seq_tokens), c_int(n_heads), c_int(kv.n_kv_heads), c_int(d), c_int(kv.window or 0), c_float(scale),
+        _ptr(tc_status(qkv.device)), _stream())

@@ -239,11 +239,23 @@ class PrefillCtx:
         self.cu_seqlens, self.seq_slot, self.seq_start = i32(cu), i32([s for s, _, _ in seqs]), i32([st for _, st, _ in seqs])
 
 
+def prefill_kernel(name):
+    return fast().attention_prefill_bf16 if name == "mma" else fast().attention_prefill_tcgen05_bf16
+
+
+def tc_status_clear():
+    st = fast().tc_status(torch.device(DEV))
+    bits = int(st.item())
+    st.zero_()
+    return bits
+
+
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
 @pytest.mark.parametrize("n_q,n_kv,d", [(8, 2, 64), (4, 4, 128), (6, 1, 128), (3, 3, 64)])
 @pytest.mark.parametrize("window", [None, 70])
-def test_attention_prefill(n_q, n_kv, d, window):
+def test_attention_prefill(n_q, n_kv, d, window, kernel):
     """Whole prompts, continuations of a cached prefix and single tokens in one launch, lengths around
-    the 16-token warp rows, the 64-token blocks and the 64-key pages; one padding sequence."""
+    the 16-token warp rows, the 64- and 128-token blocks and the 64-key pages; one padding sequence."""
     seqs = [(2, 0, 33), (0, 0, 1), (3, 95, 1), (1, 31, 34), (-1, 0, 5), (4, 64, 64), (5, 0, 200), (6, 63, 130), (7, 10, 17)]
     pages = Pages(8, 400, n_kv, d, torch.bfloat16, window=window, seed=d + n_q)
     g = gen(n_q * 10 + d)
@@ -260,8 +272,9 @@ def test_attention_prefill(n_q, n_kv, d, window):
         refs.append(plain_paged_attention(qq, k, v, start, window, scale).reshape(t, n_q * d))
     q_all = torch.cat(qs).bfloat16().to(DEV)
     out = torch.full(q_all.shape, float("nan"), dtype=torch.bfloat16, device=DEV)
-    assert fast().attention_prefill_bf16(PrefillCtx(seqs), q_all, out, pages.view, n_q, scale)
+    assert prefill_kernel(kernel)(PrefillCtx(seqs), q_all, out, pages.view, n_q, scale)
     got, ref = out.float().cpu(), torch.cat(refs)
+    assert tc_status_clear() == 0
     o = 0
     for slot, start, t in seqs:
         if slot < 0:
@@ -271,7 +284,8 @@ def test_attention_prefill(n_q, n_kv, d, window):
         o += t
 
 
-def test_attention_prefill_far_key_and_causality():
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
+def test_attention_prefill_far_key_and_causality(kernel):
     """A dominating key far back must be found by late queries and must not leak to earlier ones."""
     n_q, n_kv, d, n = 4, 2, 128, 600
     g = gen(5)
@@ -286,14 +300,74 @@ def test_attention_prefill_far_key_and_causality():
     pages = Pages(1, n, n_kv, d, torch.bfloat16)
     pages.write(0, 0, k, v)
     out = torch.empty(n, n_q * d, dtype=torch.bfloat16, device=DEV)
-    assert fast().attention_prefill_bf16(PrefillCtx([(0, 0, n)]), q.reshape(n, -1).bfloat16().to(DEV), out, pages.view,
-                                         n_q, scale)
+    assert prefill_kernel(kernel)(PrefillCtx([(0, 0, n)]), q.reshape(n, -1).bfloat16().to(DEV), out, pages.view, n_q, scale)
     got = out.float().cpu().reshape(n, n_q, d)
     kq, vq = pages.read(0, n)
     ref = plain_paged_attention(q.bfloat16().float(), kq, vq, 0, None, scale)
     assert rel_err(got, ref) < 1e-2
     assert (got[500, 0] - vq[target, 0]).abs().max() < 0.05
     assert (got[100, 2] - vq[target, 1]).abs().max() > 0.2
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("window", [None, 200])
+def test_attention_prefill_tcgen05_long_and_ragged(d, window):
+    """Several 128-token blocks per sequence, prefixes that end inside a page, a last page that is
+    partly unwritten (the cache is full of NaN there), pages before the window given back."""
+    n_q, n_kv = 6, 2
+    seqs = [(0, 0, 700), (1, 333, 400), (2, 1000, 129), (3, 64, 128), (4, 5, 255)]
+    pages = Pages(5, 1200, n_kv, d, torch.bfloat16, window=window, seed=d)
+    g = gen(d + 1)
+    scale = 1.0 / math.sqrt(d)
+    qs, refs = [], []
+    for slot, start, t in seqs:
+        n = start + t
+        k = torch.randn(n, n_kv, d, generator=g).bfloat16().float()
+        v = torch.randn(n, n_kv, d, generator=g).bfloat16().float()
+        qq = torch.randn(t, n_q, d, generator=g).bfloat16().float()
+        pages.write(slot, 0, k, v)
+        if window is not None:
+            # pages wholly before the window of the step's first new token are no longer held
+            table = pages.table.clone()
+            table[slot, :max(0, start - window + 1) // 64] = -1
+            pages.table = table
+        qs.append(qq.reshape(t, n_q * d))
+        refs.append(plain_paged_attention(qq, k, v, start, window, scale).reshape(t, n_q * d))
+    pages.view.block_table.copy_(pages.table)
+    q_all = torch.cat(qs).bfloat16().to(DEV)
+    out = torch.full(q_all.shape, float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert fast().attention_prefill_tcgen05_bf16(PrefillCtx(seqs), q_all, out, pages.view, n_q, scale)
+    got, ref = out.float().cpu(), torch.cat(refs)
+    assert tc_status_clear() == 0
+    o = 0
+    for slot, start, t in seqs:
+        assert rel_err(got[o:o + t], ref[o:o + t]) < 1e-2, (slot, start, t)
+        o += t
+
+
+def test_attention_prefill_tcgen05_rising_scores():
+    """Scores that grow from key to key by far more than the kernel lets a stale maximum lag (2^8):
+    the running maximum must be raised, and the output rescaled, tile after tile."""
+    n_q, n_kv, d, n = 2, 1, 128, 640
+    g = gen(9)
+    scale = 1.0 / math.sqrt(d)
+    u = torch.randn(d, generator=g)
+    u = u / u.norm()
+    q = (u * 8.0 * math.sqrt(d)).repeat(n, n_q, 1) + 0.1 * torch.randn(n, n_q, d, generator=g)
+    ramp = torch.linspace(-4.0, 12.0, n).reshape(n, 1, 1)                # q.k*scale runs from about -32 to 96
+    k = ramp * u.reshape(1, 1, d) + 0.05 * torch.randn(n, n_kv, d, generator=g)
+    v = torch.randn(n, n_kv, d, generator=g)
+    pages = Pages(1, n, n_kv, d, torch.bfloat16)
+    pages.write(0, 0, k, v)
+    out = torch.empty(n, n_q * d, dtype=torch.bfloat16, device=DEV)
+    assert fast().attention_prefill_tcgen05_bf16(PrefillCtx([(0, 0, n)]), q.reshape(n, -1).bfloat16().to(DEV), out, pages.view,
+                                                 n_q, scale)
+    assert tc_status_clear() == 0
+    kq, vq = pages.read(0, n)
+    ref = plain_paged_attention(q.bfloat16().float(), kq, vq, 0, None, scale)
+    got = out.float().cpu().reshape(n, n_q, d)
+    assert torch.isfinite(got).all()
+    assert rel_err(got, ref) < 1e-2
 
 
 @pytest.mark.parametrize("m", [128, 129, 255, 1000, 2100])

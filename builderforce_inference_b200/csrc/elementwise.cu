@@ -301,10 +301,13 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, long token_stride
 }
 
 // The same for bfloat16 heads of 64 or 128 values with the rotation over the whole head: a lane
-// owns 4 consecutive values (8-byte accesses) and its rotation partner sits half a head away in
-// lane ^ (LANES/2), so nothing goes through shared memory.  LANES = head_dim / 4 lanes per head;
-// a warp handles 32 / LANES heads.
-template <int D>
+// owns 8 consecutive values (16-byte accesses) and its rotation partner sits half a head away in
+// lane ^ (LANES/2), so nothing goes through shared memory.  LANES = head_dim / 8 lanes per head; a
+// warp handles QKV_UNROLL * 32 / LANES consecutive heads of one token, whose position, page and
+// rotation factors it fetches once.
+// QKV_UNROLL: heads a lane group handles, their loads in flight together (1 for few tokens, where
+// more warps matter more)
+template <int D, int QKV_UNROLL>
 __global__ void __launch_bounds__(128)
 qk_norm_rope_cache_vec_kernel(bf16* __restrict__ qkv, long token_stride, int n_tokens, int n_q, int n_kv,
                               const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w, int norm_dtype,
@@ -314,73 +317,96 @@ qk_norm_rope_cache_vec_kernel(bf16* __restrict__ qkv, long token_stride, int n_t
                               int table_stride, int flags, int* status) {
     pdl_wait();
     pdl_trigger();
-    constexpr int LANES = D / 4;
+    constexpr int LANES = D / 8;                        // a lane owns 8 consecutive values (16 bytes)
     constexpr int PER_WARP = 32 / LANES;
+    constexpr int HPW = PER_WARP * QKV_UNROLL;          // consecutive heads of one token per warp
     const int lane = threadIdx.x & 31, sub = lane % LANES;
     const int heads = n_q + 2 * n_kv;
-    const long item = ((long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * PER_WARP + lane / LANES;
-    const bool live = item < (long)n_tokens * heads;
-    const int t = live ? (int)(item / heads) : 0;
-    const int hh = live ? (int)(item - (long)t * heads) : 0;
-    const int slot = live ? token_slot[t] : -1;
-    const bool work = live && slot >= 0;
-    const int pos = work ? token_pos[t] : 0;
-    const int kind = hh < n_q ? 0 : (hh < n_q + n_kv ? 1 : 2);
-    bf16* src = qkv + (size_t)t * token_stride + (size_t)hh * D + sub * 4;
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
-    if (work) {
-        const uint2 raw = *reinterpret_cast<const uint2*>(src);
-        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-        v[0] = __low2float(lo); v[1] = __high2float(lo); v[2] = __low2float(hi); v[3] = __high2float(hi);
-    }
-    const void* nw = kind == 0 ? q_norm_w : (kind == 1 ? k_norm_w : nullptr);
-    float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+    const int groups = (heads + HPW - 1) / HPW;
+    const long item = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (long)n_tokens * groups) return;
+    const int t = (int)(item / groups);
+    const int head_base = (int)(item - (long)t * groups) * HPW + lane / LANES;
+    const int slot = token_slot[t];
+    if (slot < 0) return;
+    const int pos = token_pos[t];
+    bf16* row = qkv + (size_t)t * token_stride + sub * 8;
+
+    // every load of the warp's heads first, then the arithmetic
+    uint4 raw[QKV_UNROLL];
 #pragma unroll
-    for (int o = LANES / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if (nw != nullptr) {
-        const float scale = 1.0f / sqrtf(ss / (float)D + eps);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) v[j] = v[j] * scale * load_as_f32(nw, norm_dtype, sub * 4 + j);
+    for (int u = 0; u < QKV_UNROLL; ++u) {
+        const int hh = head_base + u * PER_WARP;
+        raw[u] = hh < heads ? *reinterpret_cast<const uint4*>(row + (size_t)hh * D) : make_uint4(0u, 0u, 0u, 0u);
     }
-    const bool rotate = kind != 2 && rope_table != nullptr;
-    bool bad_pos = false;
-    float out4[4];
+    const bool has_rope = rope_table != nullptr;
+    const bool bad_pos = has_rope && (pos < 0 || pos >= table_positions);
+    float2 cs[8];
+    float wq[8], wk[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const float other = __shfl_xor_sync(0xffffffffu, v[j], LANES / 2);
-        out4[j] = v[j];
-        if (rotate && work) {
-            if (pos < 0 || pos >= table_positions) {
-                bad_pos = true;
-            } else {
-                const bool first = sub < LANES / 2;
-                const int pair = (sub % (LANES / 2)) * 4 + j;
-                const float2 c = rope_table[(size_t)pos * (D / 2) + pair];
-                out4[j] = first ? v[j] * c.x - other * c.y : other * c.y + v[j] * c.x;
-            }
-        }
+    for (int j = 0; j < 8; ++j) {
+        cs[j] = (has_rope && !bad_pos) ? rope_table[(size_t)pos * (D / 2) + (sub % (LANES / 2)) * 8 + j] : make_float2(1.0f, 0.0f);
+        wq[j] = q_norm_w ? load_as_f32(q_norm_w, norm_dtype, sub * 8 + j) : 1.0f;
+        wk[j] = k_norm_w ? load_as_f32(k_norm_w, norm_dtype, sub * 8 + j) : 1.0f;
     }
-    if (!work) return;
+    int page = 0;
+    if (flags & 1) page = block_table[(size_t)slot * table_stride + pos / BFI_PAGE_TOKENS];
     if (bad_pos) {
-        if (sub == 0 && status) atomicOr(status, BFI_STATUS_BAD_POSITION);
+        if (lane == 0 && status) atomicOr(status, BFI_STATUS_BAD_POSITION);
         return;
     }
-    __nv_bfloat162 lo = __floats2bfloat162_rn(out4[0], out4[1]), hi = __floats2bfloat162_rn(out4[2], out4[3]);
-    uint2 packed;
-    packed.x = *reinterpret_cast<uint32_t*>(&lo);
-    packed.y = *reinterpret_cast<uint32_t*>(&hi);
-    const bool in_place = kind == 0 || (kind == 1 && (flags & 2));
-    if (in_place && (nw != nullptr || rotate)) *reinterpret_cast<uint2*>(src) = packed;
-    if (kind != 0 && (flags & 1)) {
-        const int page = block_table[(size_t)slot * table_stride + pos / BFI_PAGE_TOKENS];
-        if (page < 0) {
-            if (sub == 0 && status) atomicOr(status, BFI_STATUS_NO_PAGE);
-        } else {
+    if ((flags & 1) && page < 0 && lane == 0 && status && head_base + (QKV_UNROLL - 1) * PER_WARP >= n_q)
+        atomicOr(status, BFI_STATUS_NO_PAGE);
+
+#pragma unroll
+    for (int u = 0; u < QKV_UNROLL; ++u) {
+        const int hh = head_base + u * PER_WARP;
+        const bool live = hh < heads;
+        const int kind = hh < n_q ? 0 : (hh < n_q + n_kv ? 1 : 2);
+        const uint32_t words[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __nv_bfloat162 two = *reinterpret_cast<const __nv_bfloat162*>(&words[j]);
+            v[2 * j] = __low2float(two);
+            v[2 * j + 1] = __high2float(two);
+        }
+        const bool normed = kind == 0 ? q_norm_w != nullptr : (kind == 1 && k_norm_w != nullptr);
+        float ss = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+#pragma unroll
+        for (int o = LANES / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (normed) {
+            const float scale = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = v[j] * scale * (kind == 0 ? wq[j] : wk[j]);
+        }
+        const bool rotate = kind != 2 && has_rope;
+        float o8[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[j], LANES / 2);
+            o8[j] = v[j];
+            if (rotate) o8[j] = sub < LANES / 2 ? v[j] * cs[j].x - other * cs[j].y : other * cs[j].y + v[j] * cs[j].x;
+        }
+        if (!live) continue;
+        uint4 packed;
+        {
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(o8[0], o8[1]), p1 = __floats2bfloat162_rn(o8[2], o8[3]);
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(o8[4], o8[5]), p3 = __floats2bfloat162_rn(o8[6], o8[7]);
+            packed.x = *reinterpret_cast<uint32_t*>(&p0);
+            packed.y = *reinterpret_cast<uint32_t*>(&p1);
+            packed.z = *reinterpret_cast<uint32_t*>(&p2);
+            packed.w = *reinterpret_cast<uint32_t*>(&p3);
+        }
+        const bool in_place = kind == 0 || (kind == 1 && (flags & 2));
+        if (in_place && (normed || rotate)) *reinterpret_cast<uint4*>(row + (size_t)hh * D) = packed;
+        if (kind != 0 && (flags & 1) && page >= 0) {
             bf16* pages = kind == 1 ? k_pages : v_pages;
             const int h = kind == 1 ? hh - n_q : hh - n_q - n_kv;
-            bf16* dst = pages + (((size_t)page * n_kv + h) * BFI_PAGE_TOKENS + (pos % BFI_PAGE_TOKENS)) * D + sub * 4;
-            *reinterpret_cast<uint2*>(dst) = packed;
+            bf16* dst = pages + (((size_t)page * n_kv + h) * BFI_PAGE_TOKENS + (pos % BFI_PAGE_TOKENS)) * D + sub * 8;
+            *reinterpret_cast<uint4*>(dst) = packed;
         }
     }
 }
@@ -408,19 +434,24 @@ extern "C" int bfi_qk_norm_rope_cache(void* qkv, int dtype, long token_stride, i
     const long items = (long)n_tokens * (n_q + 2 * n_kv);
     // bfloat16 heads of 64 or 128 rotated over the whole head (or not at all): the vector kernel
     const bool vec = dtype == BFI_BF16 && (d == 64 || d == 128) && (rope_table == nullptr || rot_dim == d) &&
-                     token_stride % 4 == 0 && ((uintptr_t)qkv & 7) == 0;
+                     token_stride % 8 == 0 && ((uintptr_t)qkv & 15) == 0;
     if (vec) {
-        const int per_warp = 32 / (d / 4);
-        const long warps = (items + per_warp - 1) / per_warp;
+        const int unroll = n_tokens >= 512 ? 4 : 1;      // many tokens: more bytes in flight per warp; few: more warps
+        const int heads_per_warp = (32 / (d / 8)) * unroll;
+        const long warps = (long)n_tokens * ((n_q + 2 * n_kv + heads_per_warp - 1) / heads_per_warp);
         const int vblocks = (int)((warps + 3) / 4);
-        if (d == 128)
-            bfi_launch(qk_norm_rope_cache_vec_kernel<128>, dim3(vblocks), dim3(128), 0, stream, (bf16*)qkv, token_stride,
-                       n_tokens, n_q, n_kv, q_norm_w, k_norm_w, norm_dtype, eps, (const float2*)rope_table, table_positions,
-                       token_pos, token_slot, (bf16*)k_pages, (bf16*)v_pages, block_table, table_stride, flags, status);
-        else
-            bfi_launch(qk_norm_rope_cache_vec_kernel<64>, dim3(vblocks), dim3(128), 0, stream, (bf16*)qkv, token_stride,
-                       n_tokens, n_q, n_kv, q_norm_w, k_norm_w, norm_dtype, eps, (const float2*)rope_table, table_positions,
-                       token_pos, token_slot, (bf16*)k_pages, (bf16*)v_pages, block_table, table_stride, flags, status);
+#define BFI_QKV_VEC(DD, UU)                                                                                               \
+    bfi_launch(qk_norm_rope_cache_vec_kernel<DD, UU>, dim3(vblocks), dim3(128), 0, stream, (bf16*)qkv, token_stride,      \
+               n_tokens, n_q, n_kv, q_norm_w, k_norm_w, norm_dtype, eps, (const float2*)rope_table, table_positions,       \
+               token_pos, token_slot, (bf16*)k_pages, (bf16*)v_pages, block_table, table_stride, flags, status)
+        if (d == 128) {
+            if (unroll == 1) BFI_QKV_VEC(128, 1);
+            else BFI_QKV_VEC(128, 4);
+        } else {
+            if (unroll == 1) BFI_QKV_VEC(64, 1);
+            else BFI_QKV_VEC(64, 4);
+        }
+#undef BFI_QKV_VEC
         return bfi_check_launch("qk_norm_rope_cache_vec");
     }
     const int blocks = (int)((items + QKR_WARPS - 1) / QKR_WARPS);

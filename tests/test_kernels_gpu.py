@@ -336,6 +336,51 @@ def test_qk_norm_rope_cache(dt, n_q, n_kv, d, theta):
     assert status.item() & ops().STATUS_BAD_POSITION
 
 
+@pytest.mark.parametrize("n_q,n_kv,d", [(5, 5, 64), (6, 3, 128), (32, 8, 128), (3, 1, 64)])
+def test_qk_norm_rope_cache_many_tokens(n_q, n_kv, d):
+    """Hundreds of tokens take the variant in which a warp handles several heads of a token; head
+    counts that do not fill a warp's share, padding tokens in between, a token without a page."""
+    from builderforce_inference_b200.parts.rotary import rotary_table
+    g = gen(d + n_q)
+    theta, eps, n = 1e6, 1e-6, 700
+    pages = Pages(2, 1024, n_kv, d, torch.bfloat16)
+    qkv = (torch.randn(n, (n_q + 2 * n_kv) * d, generator=g) * 2).bfloat16()
+    qw = (1 + 0.1 * torch.randn(d, generator=g)).bfloat16()
+    kw = (1 + 0.1 * torch.randn(d, generator=g)).bfloat16()
+    pos = list(range(100, 100 + n))
+    slot = [1] * n
+    for i in (0, 13, 699):
+        slot[i] = -1                                     # padding tokens
+    table = rotary_table(theta, d, 1024, DEV)
+    dev = qkv.to(DEV).clone()
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    i32 = lambda xs: torch.tensor(xs, dtype=torch.int32, device=DEV)
+    ops().qk_norm_rope_cache(dev, n_q, n_kv, d, qw.to(DEV), kw.to(DEV), eps, table, d, i32(pos), i32(slot),
+                             pages.view, ops().FLAG_WRITE_CACHE, status)
+    assert status.item() == 0
+    x = qkv.float()
+    q = x[:, :n_q * d].reshape(n, n_q, d)
+    k = x[:, n_q * d:(n_q + n_kv) * d].reshape(n, n_kv, d)
+    v = x[:, (n_q + n_kv) * d:].reshape(n, n_kv, d)
+    q_ref = P.rope_neox(P.rms_norm(q, qw.float(), eps), pos, theta)
+    k_ref = P.rope_neox(P.rms_norm(k, kw.float(), eps), pos, theta)
+    live = [i for i in range(n) if slot[i] >= 0]
+    got_q = dev[:, :n_q * d].float().cpu().reshape(n, n_q, d)
+    assert rel_err(got_q[live], q_ref[live]) < 1e-2
+    dead = [i for i in range(n) if slot[i] < 0]
+    assert torch.equal(dev.cpu()[dead], qkv[dead])      # padding rows untouched
+    assert torch.equal(dev[:, n_q * d:].cpu(), qkv[:, n_q * d:])
+    k_got, v_got = pages.read(1, 100 + n)
+    assert rel_err(k_got[100:][live], k_ref[live]) < 1e-2
+    assert torch.equal(v_got[100:][live], v[live])
+    assert int(torch.isfinite(pages.k.float()).sum().item()) == len(live) * n_kv * d
+    # a live token whose page the sequence does not hold is recorded
+    pages.view.block_table[1, 5] = -1
+    ops().qk_norm_rope_cache(qkv.to(DEV).clone(), n_q, n_kv, d, qw.to(DEV), kw.to(DEV), eps, table, d, i32(pos), i32(slot),
+                             pages.view, ops().FLAG_WRITE_CACHE, status)
+    assert status.item() & ops().STATUS_NO_PAGE
+
+
 def test_rotation_table_against_the_formula():
     from builderforce_inference_b200.parts.rotary import rotary_table
     t = rotary_table(1e6, 128, 4096, "cpu")

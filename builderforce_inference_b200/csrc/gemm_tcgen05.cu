@@ -204,18 +204,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const int n = n0 + n_local;
             const int rank = blockIdx.z;                         // cluster dims are (1, 1, ksplit)
             const int per_rank = (BT + ksplit - 1) / ksplit;     // tokens this block finishes
-            const uint32_t local = smem_u32(smem);
+            // the same offset in every block's shared memory (at most 8 blocks in a cluster)
+            uint32_t remote[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                const uint32_t local = smem_u32(smem);
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[r]) : "r"(local), "r"(r < ksplit ? r : 0));
+            }
             for (int j = rank * per_rank; j < min(BT, (rank + 1) * per_rank); ++j) {
                 const int m = m0 + j;
                 if (m >= M) break;
-                float v = 0.0f;
-                for (int r = 0; r < ksplit; ++r) {
-                    uint32_t remote;
-                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(r));
-                    float x;
-                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(x) : "r"(remote + (uint32_t)(j * TC_ROWS + n_local) * 4));
-                    v += x;
+                // all splits' loads first, then the sum in split order
+                float x[8];
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    x[r] = 0.0f;
+                    if (r < ksplit)
+                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(x[r]) : "r"(remote[r] + (uint32_t)(j * TC_ROWS + n_local) * 4));
                 }
+                float v = 0.0f;
+#pragma unroll
+                for (int r = 0; r < 8; ++r) v += x[r];
                 if (epilogue == EPI_SWIGLU) {
                     const float up = __shfl_down_sync(0xffffffffu, v, 1);
                     if ((lane & 1) == 0 && n + 1 < N)

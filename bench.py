@@ -259,15 +259,21 @@ def kernel_run(a) -> int:
         one(i)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    graph = torch.cuda.CUDAGraph()          # one graph of all launches: no host gaps between short kernels
-    with torch.cuda.graph(graph):
+    if a.eager:                             # plain launches (for captures under ncu)
+        e0.record()
         for i in range(reps):
             one(i)
-    graph.replay()
-    torch.cuda.synchronize()
-    e0.record()
-    graph.replay()
-    e1.record()
+        e1.record()
+    else:
+        graph = torch.cuda.CUDAGraph()      # one graph of all launches: no host gaps between short kernels
+        with torch.cuda.graph(graph):
+            for i in range(reps):
+                one(i)
+        graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        graph.replay()
+        e1.record()
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / reps
     pk = peaks()
@@ -275,7 +281,8 @@ def kernel_run(a) -> int:
                       "GB_s": round(bytes_moved / us / 1e3, 1), "TFLOP_s": round(flops / us / 1e6, 1),
                       "frac_hbm": round(bytes_moved / us / 1e3 / pk["hbm_gbs"], 3),
                       "frac_bf16": round(flops / us / 1e6 / pk["bf16_tflops"], 3), "peaks": pk["source"],
-                      "note": "launches replayed from one CUDA graph, operands rotating over more than L2"}))
+                      "note": ("plain launches: short kernels include launch gaps" if a.eager else
+                               "launches replayed from one CUDA graph") + ", operands rotating over more than L2"}))
     return 0
 
 
@@ -285,6 +292,7 @@ def main() -> int:
                                                        "attention_prefill", "attention_prefill_tcgen05"],
                     help="time one kernel instead of the model (see kernel_run)")
     ap.add_argument("--shape", default="qkv", choices=sorted(KERNEL_SHAPES))
+    ap.add_argument("--eager", action="store_true", help="with --kernel: plain launches instead of one CUDA graph")
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=2048)
     ap.add_argument("--gpus", type=int, default=1)

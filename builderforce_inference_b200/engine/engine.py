@@ -20,6 +20,7 @@ import os
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..cache.cache import SequenceCache
@@ -170,9 +171,18 @@ class Engine:
             n = len(s.tokens)
             if n == 0:
                 raise StepError(f"slot {s.slot}: empty token list")
-            for t in s.tokens:
-                if not 0 <= int(t) < vocab:
-                    raise StepError(f"slot {s.slot}: token id {t} out of range for vocabulary {vocab}")
+            if n > 16:
+                try:
+                    arr = np.asarray(s.tokens, dtype=np.int64)
+                except (OverflowError, ValueError, TypeError) as e:
+                    raise StepError(f"slot {s.slot}: token ids must be integers below the vocabulary {vocab}: {e}") from e
+                bad = np.nonzero((arr < 0) | (arr >= vocab))[0]
+                if bad.size:
+                    raise StepError(f"slot {s.slot}: token id {int(arr[bad[0]])} out of range for vocabulary {vocab}")
+            else:
+                for t in s.tokens:
+                    if not 0 <= int(t) < vocab:
+                        raise StepError(f"slot {s.slot}: token id {t} out of range for vocabulary {vocab}")
             for w in s.want:
                 if not 0 <= int(w) < n:
                     raise StepError(f"slot {s.slot}: wanted place {w} is not among its {n} tokens")
@@ -272,15 +282,16 @@ class Engine:
             want_base.append(acc)
             acc += len(s.want)
         for piece in pieces:
-            tok, pos, slot_of, cu, p_slots, p_starts, p_counts = [], [], [], [0], [], [], []
+            tok_parts, pos_parts, slot_parts = [], [], []
+            cu, p_slots, p_starts, p_counts = [0], [], [], []
             rows, dest = [], []
             for (i, off, take) in piece:
                 s = seqs[i]
-                base = len(tok)
-                tok.extend(int(t) for t in s.tokens[off:off + take])
-                pos.extend(range(starts[i] + off, starts[i] + off + take))
-                slot_of.extend([slots[i]] * take)
-                cu.append(len(tok))
+                base = cu[-1]
+                tok_parts.append(np.asarray(s.tokens[off:off + take], dtype=np.int32))
+                pos_parts.append(np.arange(starts[i] + off, starts[i] + off + take, dtype=np.int32))
+                slot_parts.append(np.full(take, slots[i], dtype=np.int32))
+                cu.append(base + take)
                 p_slots.append(slots[i])
                 p_starts.append(starts[i] + off)
                 p_counts.append(take)
@@ -288,7 +299,8 @@ class Engine:
                     if off <= w < off + take:
                         rows.append(base + (w - off))
                         dest.append(want_base[i] + j)
-            n_tok, n_seq = len(tok), len(piece)
+            tok, pos, slot_of = np.concatenate(tok_parts), np.concatenate(pos_parts), np.concatenate(slot_parts)
+            n_tok, n_seq = cu[-1], len(piece)
             meta = self._meta_buffer(n_tok, n_seq, len(rows))
             self._fill_meta(meta, tok, pos, slot_of, cu, n_tok, n_seq, p_slots, p_starts, rows)
             ctx = self._context_from_meta(meta, n_tok, n_seq, max(p_counts), (p_slots, p_starts, p_counts))
@@ -340,14 +352,15 @@ class Engine:
         pad_t = n_tok - len(tok)
         pad_s = n_seq - len(seq_slots)
         last = cu[-1]
-        host = (list(tok) + [0] * pad_t + list(pos) + [0] * pad_t + list(slot_of) + [-1] * pad_t
-                + list(cu) + [last] * pad_s + list(seq_slots) + [-1] * pad_s
-                + list(seq_starts) + [0] * pad_s
-                # pages the sequences hold after this step, summed: kernels size their work split by it
-                + [sum((int(st) + (int(cu[i + 1]) - int(cu[i])) + PAGE_TOKENS - 1) // PAGE_TOKENS
-                       for i, st in enumerate(seq_starts))]
-                + list(want_rows))
-        n = len(host)
+        # pages the sequences hold after this step, summed: kernels size their work split by it
+        pages = sum((int(st) + (int(cu[i + 1]) - int(cu[i])) + PAGE_TOKENS - 1) // PAGE_TOKENS
+                    for i, st in enumerate(seq_starts))
+        i32 = lambda xs: np.asarray(xs, dtype=np.int32)
+        host = np.concatenate([
+            i32(tok), np.zeros(pad_t, np.int32), i32(pos), np.zeros(pad_t, np.int32), i32(slot_of), np.full(pad_t, -1, np.int32),
+            i32(cu), np.full(pad_s, last, np.int32), i32(seq_slots), np.full(pad_s, -1, np.int32),
+            i32(seq_starts), np.zeros(pad_s, np.int32), i32([pages]), i32(want_rows)])
+        n = host.shape[0]
         pinned = self._pinned.get(n)
         if pinned is None:
             pinned = torch.empty(n, dtype=torch.int32, pin_memory=True)
@@ -355,7 +368,7 @@ class Engine:
         else:
             # the previous copy from this buffer must have been consumed before it is rewritten
             torch.cuda.current_stream(self.device).synchronize()
-        pinned.copy_(torch.tensor(host, dtype=torch.int32))
+        pinned.numpy()[:] = host
         meta[:n].copy_(pinned, non_blocking=True)
         self.last_h2d_bytes = 4 * n
 

@@ -37,7 +37,13 @@ def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
     return c_void_p(0) if t is None else c_void_p(t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> c_void_p:
+    """The current CUDA stream of the current device, as a handle for the launchers."""
+    if _raw_stream is not None:
+        return c_void_p(_raw_stream(torch.cuda.current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 

@@ -261,29 +261,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 }
 
 // ------------------------------------------------------------------------------------------
-// Many tokens (prompts): tokens on the lanes.  D[128 tokens, 256 features] per tile, so a thread
+// Many tokens (prompts): tokens on the lanes.  D[128 tokens, tile_n features] per tile, so a thread
 // holds 16 consecutive features of one token after tcgen05.ld and stores them as whole 16-byte
 // words (and SiLU*mul pairs sit in one thread).  The kernel is persistent: each block walks over
 // tiles, and the two halves of tensor memory (2 x 256 columns) alternate as accumulators, so the
-// epilogue of one tile runs while the tensor cores work on the next.
+// epilogue of one tile runs while the tensor cores work on the next.  tile_n (a multiple of 16, at
+// most 256) is chosen per product so that the tiles fill whole rounds of the SMs: 2560 features
+// x 2048 tokens are 160 tiles of 256 (two rounds, the second almost empty) but 288 tiles of 144.
 //   barriers: full/empty per ring stage, tmem_full/tmem_empty per accumulator
 // ------------------------------------------------------------------------------------------
 #define TP_TOKENS 128
-#define TP_FEATS 256
-#define TP_STAGE_BYTES ((TP_TOKENS + TP_FEATS) * TC_BK * 2)      // 48 KB
-#define TP_STAGES 4
-#define TP_SMEM ((size_t)TP_STAGES * TP_STAGE_BYTES + 1024 + 256)
+#define TP_FEATS 256                                             // widest tile; the accumulators' stride
+#define TP_RING_BYTES (4 * (TP_TOKENS + TP_FEATS) * TC_BK * 2)   // 192 KB
+#define TP_MAX_STAGES 8
+#define TP_SMEM ((size_t)TP_RING_BYTES + 1024 + 256)
 
 
+template <int HALVES>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                             void* __restrict__ C, int c_dtype, long ldc, int M, int N, int K, int tiles_m, int tiles_n,
-                            int epilogue, int vec_ok, int* __restrict__ status) {
+                            int tile_n, int n_stages, int epilogue, int vec_ok, int* __restrict__ status) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)TP_STAGES * TP_STAGE_BYTES);
-    uint64_t* empty = full + TP_STAGES;
-    uint64_t* tmem_full = empty + TP_STAGES;      // [2]
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)TP_RING_BYTES);
+    uint64_t* empty = full + TP_MAX_STAGES;
+    uint64_t* tmem_full = empty + TP_MAX_STAGES;  // [2]
+    constexpr int TILE_TOKENS = HALVES * TP_TOKENS;
+    const uint32_t stage_bytes = (uint32_t)(TILE_TOKENS + tile_n) * TC_BK * 2;  // a multiple of 2048
     uint64_t* tmem_empty = tmem_full + 2;         // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
     int* s_flag = reinterpret_cast<int*>(tmem_slot + 1);
@@ -293,7 +298,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     const int n_tiles = tiles_m * tiles_n;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < TP_STAGES; ++s) {
+        for (int s = 0; s < n_stages; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
@@ -332,66 +337,79 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                 int tm, tn;
                 tile_coords(tile, tm, tn);
                 for (int i = 0; i < n_kb; ++i, ++it) {
-                    const int s = it % TP_STAGES;
-                    const uint32_t phase = (it / TP_STAGES) & 1;
-                    if (it >= TP_STAGES && !mbar_wait(&empty[s], phase ^ 1)) {
+                    const int s = it % n_stages;
+                    const uint32_t phase = (it / n_stages) & 1;
+                    if (it >= n_stages && !mbar_wait(&empty[s], phase ^ 1)) {
                         atomicOr(status, BFI_STATUS_TIMEOUT);
                         s_flag[0] = 1;
                         break;
                     }
-                    unsigned char* stage = smem + (size_t)s * TP_STAGE_BYTES;
-                    mbar_expect_tx(&full[s], TP_STAGE_BYTES);
-                    tma_load_2d(stage, &map_a, i * TC_BK, tm * TP_TOKENS, &full[s]);
-                    tma_load_2d(stage + TP_TOKENS * TC_BK * 2, &map_w, i * TC_BK, tn * TP_FEATS, &full[s]);
+                    unsigned char* stage = smem + (size_t)s * stage_bytes;
+                    mbar_expect_tx(&full[s], stage_bytes);
+                    tma_load_2d(stage, &map_a, i * TC_BK, tm * TILE_TOKENS, &full[s]);
+                    tma_load_2d(stage + TILE_TOKENS * TC_BK * 2, &map_w, i * TC_BK, tn * tile_n, &full[s]);
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc(TP_TOKENS, TP_FEATS);
+            const uint32_t idesc = umma_idesc(TP_TOKENS, tile_n);
             int it = 0, local = 0;
             for (int tile = blockIdx.x; tile < n_tiles && !s_flag[0]; tile += gridDim.x, ++local) {
+                // HALVES == 1: the two accumulators alternate between tiles.  HALVES == 2: a tile's two
+                // token halves own one accumulator each, and a half may be overwritten as soon as the
+                // epilogue has drained it.
                 const int acc = local & 1;
-                const uint32_t use = (uint32_t)(local >> 1);       // how often this accumulator was used before
-                if (local >= 2 && !mbar_wait(&tmem_empty[acc], (use & 1) ^ 1)) {
-                    atomicOr(status, BFI_STATUS_TIMEOUT);
-                    s_flag[0] = 1;
-                    break;
-                }
-                tc_fence_after();
-                const uint32_t d_addr = tmem_base + (uint32_t)acc * TP_FEATS;
                 bool ok = true;
-                for (int i = 0; i < n_kb; ++i, ++it) {
-                    const int s = it % TP_STAGES;
-                    const uint32_t phase = (it / TP_STAGES) & 1;
+                if (HALVES == 1 && local >= 2 && !mbar_wait(&tmem_empty[acc], (((uint32_t)(local >> 1)) & 1) ^ 1)) ok = false;
+                tc_fence_after();
+                for (int i = 0; ok && i < n_kb; ++i, ++it) {
+                    const int s = it % n_stages;
+                    const uint32_t phase = (it / n_stages) & 1;
                     if (!mbar_wait(&full[s], phase)) {
-                        atomicOr(status, BFI_STATUS_TIMEOUT);
-                        s_flag[0] = 1;
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t aa = smem_u32(smem + (size_t)s * TP_STAGE_BYTES);
-                    const uint32_t wa = aa + TP_TOKENS * TC_BK * 2;
+                    const uint32_t aa = smem_u32(smem + (size_t)s * stage_bytes);
+                    const uint32_t wa = aa + TILE_TOKENS * TC_BK * 2;
 #pragma unroll
-                    for (int kk = 0; kk < TC_BK / 16; ++kk)
-                        umma_bf16(d_addr, umma_desc_sw128(aa + kk * 32), umma_desc_sw128(wa + kk * 32), idesc,
-                                  (i > 0 || kk > 0) ? 1u : 0u);
+                    for (int h = 0; h < HALVES; ++h) {
+                        if (HALVES == 2 && i == 0 && local >= 1) {
+                            if (!mbar_wait(&tmem_empty[h], (uint32_t)((local - 1) & 1))) {
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after();
+                        }
+                        const uint32_t d_addr = tmem_base + (uint32_t)(HALVES == 1 ? acc : h) * TP_FEATS;
+                        const uint32_t ah = aa + h * TP_TOKENS * TC_BK * 2;
+#pragma unroll
+                        for (int kk = 0; kk < TC_BK / 16; ++kk)
+                            umma_bf16(d_addr, umma_desc_sw128(ah + kk * 32), umma_desc_sw128(wa + kk * 32), idesc,
+                                      (i > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    if (!ok) break;
                     umma_commit(&empty[s]);
                 }
-                umma_commit(&tmem_full[acc]);
-                if (!ok) break;
+                umma_commit(&tmem_full[HALVES == 1 ? acc : 0]);
+                if (!ok) {
+                    atomicOr(status, BFI_STATUS_TIMEOUT);
+                    s_flag[0] = 1;
+                    break;
+                }
             }
         }
     } else {
         const int quad = warp & 3;
         int local = 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
-            const int acc = local & 1;
-            const uint32_t use = (uint32_t)(local >> 1);
+        bool alive = true;
+        for (int tile = blockIdx.x; alive && tile < n_tiles; tile += gridDim.x, ++local) {
             int tm, tn;
             tile_coords(tile, tm, tn);
-            if (!mbar_wait(&tmem_full[acc], use & 1)) {
+            const int full_idx = HALVES == 1 ? (local & 1) : 0;
+            const uint32_t full_parity = HALVES == 1 ? (uint32_t)((local >> 1) & 1) : (uint32_t)(local & 1);
+            if (!mbar_wait(&tmem_full[full_idx], full_parity)) {
                 if (lane == 0) {
                     atomicOr(status, BFI_STATUS_TIMEOUT);
                     s_flag[0] = 1;
@@ -399,11 +417,13 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                 break;
             }
             tc_fence_after();
-            const int m = tm * TP_TOKENS + quad * 32 + lane;
+            for (int h = 0; h < HALVES; ++h) {
+            const int acc = HALVES == 1 ? (local & 1) : h;
+            const int m = tm * TILE_TOKENS + h * TP_TOKENS + quad * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * TP_FEATS;
 #pragma unroll 1
-            for (int c = 0; c < TP_FEATS / 16; ++c) {
-                const int n = tn * TP_FEATS + c * 16;
+            for (int c = 0; c < tile_n / 16; ++c) {
+                const int n = tn * tile_n + c * 16;
                 if (n >= N) break;
                 float v[16];
                 tmem_ld16(taddr + c * 16, v);
@@ -476,6 +496,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+            }
         }
     }
 
@@ -483,7 +504,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     __syncthreads();
     if (s_flag[0] && warp == 0 && lane == 0) {
         // a wait ran out: give outstanding TMA writes a bounded time to land
-        for (int s = 0; s < TP_STAGES; ++s) mbar_wait(&full[s], 0), mbar_wait(&full[s], 1);
+        for (int s = 0; s < n_stages; ++s) mbar_wait(&full[s], 0), mbar_wait(&full[s], 1);
     }
     __syncthreads();
     if (warp == 1) {
@@ -633,18 +654,24 @@ static int launch_tc(const TcPlan& p, const CUtensorMap& mw, const CUtensorMap& 
     return bfi_check_launch("gemm_tcgen05");
 }
 
+// tests and experiments: force the tile of the persistent kernel (0 = choose): features per tile,
+// and one or two halves of 128 tokens
+static int g_tp_tune_tile_n = 0, g_tp_tune_halves = 0;
+extern "C" int bfi_gemm_tcgen05_tune_tile(int tile_n, int halves) {
+    g_tp_tune_tile_n = (tile_n >= 16 && tile_n <= TP_FEATS && tile_n % 16 == 0) ? tile_n : 0;
+    g_tp_tune_halves = (halves == 1 || halves == 2) ? halves : 0;
+    return 0;
+}
+
 static int launch_tc_prefill(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype, long ldc, int M,
                              int N, int K, int epilogue, int* status, cudaStream_t stream) {
-    CUtensorMap ma, mw;
-    int rc = bfi_tensor_map_bf16(A, M, K, lda, TP_TOKENS, &ma);
-    if (rc) return rc;
-    rc = bfi_tensor_map_bf16(W, N, K, ldw, TP_FEATS, &mw);
-    if (rc) return rc;
     static bool configured = false;
     static int n_sm = 148;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_prefill_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)TP_SMEM);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemm_tcgen05_prefill_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TP_SMEM);
         if (e != cudaSuccess)
             return bfi_fail("gemm_tcgen05: cannot reserve %zu bytes of shared memory: %s", (size_t)TP_SMEM, cudaGetErrorString(e));
         int dev = 0;
@@ -652,16 +679,56 @@ static int launch_tc_prefill(const void* A, long lda, const void* W, long ldw, v
         cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
         configured = true;
     }
-    const int tiles_m = (M + TP_TOKENS - 1) / TP_TOKENS, tiles_n = (N + TP_FEATS - 1) / TP_FEATS;
+    // The tile (one or two halves of 128 tokens x tile_n features) that takes the least time by an
+    // estimate fitted to measurements: rounds over the SMs x (k blocks x the time of a k block, which
+    // grows slowly with the width and is 1.4 x longer for two halves, + a tile's share that no other
+    // tile hides: little when the accumulators alternate, the whole epilogue when a tile owns both).
+    int halves = 1, tile_n = TP_FEATS;
+    {
+        const double n_kb = (double)((K + TC_BK - 1) / TC_BK);
+        double best = -1.0;
+        for (int h = 1; h <= (M > TP_TOKENS ? 2 : 1); ++h) {
+            if (g_tp_tune_halves && h != g_tp_tune_halves) continue;
+            for (int tn = TP_FEATS; tn >= 128; tn -= 16) {
+                if (g_tp_tune_tile_n && tn != g_tp_tune_tile_n) continue;
+                const long t = (long)((M + h * TP_TOKENS - 1) / (h * TP_TOKENS)) * ((N + tn - 1) / tn);
+                const double kb_time = (h == 1 ? 0.351 : 0.507) + 0.00048 * tn;
+                const double cost = (double)((t + n_sm - 1) / n_sm) * (n_kb * kb_time + (h == 1 ? 2.0 : 10.0));
+                if (best < 0.0 || cost < best) {
+                    best = cost;
+                    halves = h;
+                    tile_n = tn;
+                }
+            }
+        }
+        if (best < 0.0) {               // a forced width below 128
+            tile_n = g_tp_tune_tile_n;
+            halves = g_tp_tune_halves ? g_tp_tune_halves : 1;
+        }
+    }
+    const int tile_tokens = halves * TP_TOKENS;
+    const int tiles_m = (M + tile_tokens - 1) / tile_tokens, tiles_n = (N + tile_n - 1) / tile_n;
     const long tiles = (long)tiles_m * tiles_n;
     const int grid = (int)(tiles < n_sm ? tiles : n_sm);
+    const int stage_bytes = (tile_tokens + tile_n) * TC_BK * 2;
+    int n_stages = TP_RING_BYTES / stage_bytes;
+    if (n_stages > TP_MAX_STAGES) n_stages = TP_MAX_STAGES;
+    CUtensorMap ma, mw;
+    int rc = bfi_tensor_map_bf16(A, M, K, lda, tile_tokens, &ma);
+    if (rc) return rc;
+    rc = bfi_tensor_map_bf16(W, N, K, ldw, tile_n, &mw);
+    if (rc) return rc;
     // whole 16-byte stores need aligned rows: output row stride and base
     const int out_cols_shift = epilogue == EPI_SWIGLU ? 1 : 0;
     (void)out_cols_shift;
     const int elem = dtype_size(c_dtype);
     const int vec_ok = ((ldc * elem) % 16 == 0 && ((uintptr_t)C & 15) == 0) ? 1 : 0;
-    bfi_launch(gemm_tcgen05_prefill_kernel, dim3(grid), dim3(TC_THREADS), TP_SMEM, stream, ma, mw, C, c_dtype, ldc, M, N, K,
-               tiles_m, tiles_n, epilogue, vec_ok, status);
+    if (halves == 2)
+        bfi_launch(gemm_tcgen05_prefill_kernel<2>, dim3(grid), dim3(TC_THREADS), TP_SMEM, stream, ma, mw, C, c_dtype, ldc, M, N,
+                   K, tiles_m, tiles_n, tile_n, n_stages, epilogue, vec_ok, status);
+    else
+        bfi_launch(gemm_tcgen05_prefill_kernel<1>, dim3(grid), dim3(TC_THREADS), TP_SMEM, stream, ma, mw, C, c_dtype, ldc, M, N,
+                   K, tiles_m, tiles_n, tile_n, n_stages, epilogue, vec_ok, status);
     return bfi_check_launch("gemm_tcgen05_prefill");
 }
 

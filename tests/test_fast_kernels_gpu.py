@@ -378,6 +378,23 @@ def test_gemm_tcgen05_many_tokens(m, n, k, epi):
     tc_check(m, n, k, epi, seed=7)
 
 
+@pytest.mark.parametrize("halves", [1, 2])
+@pytest.mark.parametrize("tile_n", [128, 144, 176, 240, 256])
+@pytest.mark.parametrize("m,n,k,epi", [(300, 2560, 512, 1), (129, 1000, 200, 0), (640, 2000, 1024, 2), (1500, 700, 4096, 0)])
+def test_gemm_tcgen05_many_tokens_every_tile(tile_n, halves, m, n, k, epi):
+    """The persistent kernel's tile (128 or 256 tokens x 128..256 features) is chosen per product;
+    every tile gives the same result, with several tiles per block and ragged edges."""
+    import ctypes
+    from builderforce_inference_b200.kernels.library import library
+    lib = library("fast").lib
+    lib.bfi_gemm_tcgen05_tune_tile(ctypes.c_int(tile_n), ctypes.c_int(halves))
+    try:
+        tc_check(m, n, k, epi, seed=tile_n + halves)
+    finally:
+        lib.bfi_gemm_tcgen05_tune_tile(ctypes.c_int(0), ctypes.c_int(0))
+    assert tc_status_clear() == 0
+
+
 def test_gemm_tcgen05_many_tokens_unaligned_output_rows():
     """An output whose rows are not 16-byte aligned takes the scalar stores and is still right."""
     m, n, k = 300, 200, 512

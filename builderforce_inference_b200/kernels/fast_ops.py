@@ -131,11 +131,11 @@ FUSED_MERGE_MAX_GROUPS = 16
 
 
 def decode_splits(n_seqs: int, n_kv: int, group: int, max_pages: int) -> int:
-    """Into how many page ranges every (sequence, kv head) is cut: enough blocks to fill the GPU a
-    few times over, never more than a sequence can have pages.  Depends only on sizes that are
+    """Into how many page ranges every (sequence, kv head) is cut: enough blocks to fill the GPU
+    once, never more than a sequence can have pages.  Depends only on sizes that are
     fixed when a step is captured."""
     blocks = n_seqs * n_kv * ((group + 15) // 16)
-    want = (SM_COUNT * 4 + blocks - 1) // blocks
+    want = (SM_COUNT * 3 + blocks - 1) // blocks          # three blocks are resident on an SM: one wave
     return max(1, min(want, max_pages, 32))
 
 

@@ -212,6 +212,32 @@ def argmax_rows(logits: torch.Tensor, out: torch.Tensor, scratch: Optional[torch
                          c_int(logits.shape[1]), _ptr(out), _ptr(scratch), c_long(n_scratch), _stream())
 
 
+def sample_sorted_rows(logits: torch.Tensor, temperature: torch.Tensor, u: torch.Tensor, out: torch.Tensor,
+                       probs: torch.Tensor, top_k: int = 0, top_p: float = 1.0, repeat_penalty: float = 1.0,
+                       presence_penalty: float = 0.0, min_p: float = 0.0, seen: Optional[torch.Tensor] = None,
+                       seen_cu: Optional[torch.Tensor] = None, work: Optional[torch.Tensor] = None) -> None:
+    """Top-k / top-p sampling in the reference's order (probability descending, index ascending)
+    without a sort; ``probs`` is float32 scratch ``[rows, vocab]``."""
+    _need_cuda(logits, temperature, u, out, probs, seen, seen_cu, work)
+    _rows_2d(logits, "logits")
+    _i32(out, "sample output")
+    _i32(seen, "seen ids")
+    _i32(seen_cu, "seen offsets")
+    rows, vocab = logits.shape
+    for t, what in ((temperature, "temperature"), (u, "uniform draws")):
+        if t.dtype != torch.float32 or not t.is_contiguous() or t.numel() < rows:
+            raise KernelError(f"{what} must be contiguous float32 with one value per row")
+    if logits.dtype != torch.float32 or out.numel() < rows:
+        raise KernelError("sample: logits must be float32 and the output hold one id per row")
+    for buf, what in ((probs, "probability"), (work, "work")):
+        if buf is not None and (buf.dtype != torch.float32 or not buf.is_contiguous() or buf.numel() < rows * vocab):
+            raise KernelError(f"sample: {what} buffer must be contiguous float32 [rows, vocab]")
+    library("core").call("bfi_sample_sorted_rows", _ptr(logits), c_long(logits.stride(0)), _ptr(work), _ptr(probs),
+                         c_int(rows), c_int(vocab), _ptr(seen), _ptr(seen_cu), _ptr(temperature), _ptr(u),
+                         c_float(repeat_penalty), c_float(presence_penalty), c_int(int(top_k)), c_float(top_p),
+                         c_float(min_p), _ptr(out), _stream())
+
+
 def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, u: torch.Tensor, out: torch.Tensor,
                 repeat_penalty: float = 1.0, presence_penalty: float = 0.0, min_p: float = 0.0,
                 seen: Optional[torch.Tensor] = None, seen_cu: Optional[torch.Tensor] = None,

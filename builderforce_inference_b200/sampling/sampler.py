@@ -1,9 +1,9 @@
 """Choosing next tokens on the device.
 
-Greedy, temperature, penalties and min-p run in this package's kernels (``sample_rows``,
-``argmax_rows``).  Top-k and top-p, which need the probabilities in descending order
-(crates/bfi-runtime/src/sample.rs:392-409), sort with the tensor library and then draw exactly as
-the reference does: in list order, which after a sort is descending probability.
+Everything runs in this package's kernels: greedy (``argmax_rows``), temperature with penalties
+and min-p, drawn in vocabulary order (``sample_rows``), and top-k / top-p, whose kept set and draw
+follow the reference's order after its stable sort (probability descending, index ascending,
+crates/bfi-runtime/src/sample.rs:392-409) and are found without sorting (``sample_sorted_rows``).
 
 The uniform number of a draw depends on (seed, request index, step), so a run is reproducible
 and every step and request draws its own number.  The reference restarts its generator from the
@@ -47,6 +47,7 @@ class Sampler:
         self.vocab = vocab_size
         self._out = torch.empty(0, dtype=torch.int32, device=device)
         self._work: Optional[torch.Tensor] = None
+        self._probs: Optional[torch.Tensor] = None
         self._scratch = torch.empty(0, dtype=torch.int32, device=device)
 
     def _out_rows(self, n: int) -> torch.Tensor:
@@ -85,49 +86,14 @@ class Sampler:
                 if self._work is None or self._work.numel() < rows * self.vocab:
                     self._work = torch.empty(rows * self.vocab, dtype=torch.float32, device=self.device)
                 work = self._work
-        if params.needs_sort:
-            return self._sample_sorted(logits, params, u, seen, seen_cu, out)
         temp = torch.full((rows,), float(params.temperature), dtype=torch.float32, device=self.device)
         ut = torch.tensor(u, dtype=torch.float32, device=self.device)
+        if params.needs_sort:
+            if self._probs is None or self._probs.numel() < rows * self.vocab:
+                self._probs = torch.empty(rows * self.vocab, dtype=torch.float32, device=self.device)
+            ops.sample_sorted_rows(logits, temp, ut, out, self._probs, params.top_k, params.top_p, params.repeat_penalty,
+                                   params.presence_penalty, params.min_p, seen, seen_cu, work)
+            return out
         ops.sample_rows(logits, temp, ut, out, params.repeat_penalty, params.presence_penalty, params.min_p,
                         seen, seen_cu, work)
-        return out
-
-    def _sample_sorted(self, logits, params: SampleParams, u, seen, seen_cu, out) -> torch.Tensor:
-        """Top-k / top-p: penalties, softmax, descending sort, cuts, min-p, draw in sorted order."""
-        x = logits.clone()
-        if seen is not None:
-            cu = seen_cu.tolist()
-            for r in range(x.shape[0]):
-                ids = seen[cu[r]:cu[r + 1]].long()
-                if ids.numel() == 0:
-                    continue
-                v = x[r, ids]
-                if abs(params.repeat_penalty - 1.0) > 1.1920929e-07:
-                    v = torch.where(v > 0, v / params.repeat_penalty, v * params.repeat_penalty)
-                x[r, ids] = v - params.presence_penalty
-        x = x / params.temperature
-        p = torch.softmax(x, dim=-1)
-        sp, si = torch.sort(p, dim=-1, descending=True, stable=True)
-        keep = torch.ones_like(sp, dtype=torch.bool)
-        if params.top_k > 0 and params.top_k < sp.shape[1]:
-            keep[:, params.top_k:] = False
-        if params.top_p < 1.0:
-            cum = torch.cumsum(sp * keep, dim=-1)
-            # keep through the first position whose running sum reaches top_p (at least one)
-            before = cum - sp * keep
-            keep &= before < params.top_p
-            keep[:, 0] = True
-        if params.min_p > 0.0:
-            keep &= sp >= params.min_p * sp[:, :1]
-        w = sp * keep
-        total = w.sum(dim=-1, keepdim=True)
-        r = torch.tensor(u, dtype=torch.float32, device=logits.device)[:, None] * total
-        cumw = torch.cumsum(w, dim=-1)
-        hit = (cumw >= r) & keep
-        first = torch.argmax(hit.int(), dim=-1)
-        none = ~hit.any(dim=-1)
-        last_kept = keep.int().cumsum(dim=-1).argmax(dim=-1)
-        first = torch.where(none, last_kept, first)
-        out.copy_(si.gather(1, first[:, None]).squeeze(1).to(torch.int32))
         return out

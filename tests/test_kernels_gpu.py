@@ -430,6 +430,79 @@ def test_temperature_sampling_follows_the_plain_cdf(vocab):
         assert tok == plain_tok or abs(us[r] - lo) < 1e-5 or abs(us[r] - cdf[tok].item()) < 1e-5
 
 
+def _sorted_sample(x, us, temp, probs=None, **kw):
+    rows, vocab = x.shape
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    probs = torch.empty(rows * vocab, device=DEV) if probs is None else probs
+    ops().sample_sorted_rows(x.to(DEV), torch.full((rows,), temp, device=DEV), torch.tensor(us, device=DEV), out, probs, **kw)
+    return out.tolist()
+
+
+@pytest.mark.parametrize("vocab", [37, 384, 5000])
+@pytest.mark.parametrize("cuts", [dict(top_k=12), dict(top_p=0.8), dict(top_k=50, top_p=0.6), dict(top_p=0.95, min_p=0.02),
+                                  dict(top_k=1), dict(top_p=0.0), dict(top_k=3, min_p=0.9)])
+def test_top_k_top_p_sampling_follows_the_plain_order(vocab, cuts):
+    """The kept set and the draw in the reference's order (probability descending, index ascending)
+    against the plain sampler, which sorts; a uniform number may differ only on the edge of an interval."""
+    g = gen(vocab + len(cuts))
+    rows, temp = 24, 0.9
+    x = torch.randn(rows, vocab, generator=g) * 2
+    us = torch.rand(rows, generator=g).tolist()
+    us[0], us[1] = 0.0, 0.9999999
+    got = _sorted_sample(x, us, temp, **cuts)
+    for r in range(rows):
+        kind, pairs = P.target(x[r].tolist(), [], P.PlainSampleParams(temperature=temp, **cuts))
+        assert kind == "weights"
+        assert got[r] in [i for i, _ in pairs], (r, "a token outside the kept set")
+        total = sum(w for _, w in pairs)
+        cum = 0.0
+        for i, w in pairs:
+            lo, cum = cum, cum + w
+            if i == got[r]:
+                assert lo - 1e-5 * total <= us[r] * total <= cum + 1e-5 * total, (r, got[r], us[r])
+
+
+def test_top_k_top_p_sampling_with_ties_penalties_and_a_large_vocabulary():
+    # ties: equal logits are ordered by index, so top_k = 3 over five equal maxima keeps the first three
+    vocab = 64
+    x = torch.full((1, vocab), -5.0)
+    for i in (40, 7, 22, 9, 63):
+        x[0, i] = 3.0
+    for u, want in ((0.0, 7), (0.34, 9), (0.67, 22), (0.999, 22)):
+        assert _sorted_sample(x, [u], 1.0, top_k=3) == [want]
+        kind, pairs = P.target(x[0].tolist(), [], P.PlainSampleParams(temperature=1.0, top_k=3))
+        assert [i for i, _ in pairs] == [7, 9, 22] and P.draw(pairs, u) == want
+    # top_p over the same ties: 0.5 of the mass needs three of the five (each holds a fifth, nearly)
+    assert _sorted_sample(x, [0.999], 1.0, top_p=0.5) == [22]
+    # penalties first: the seen maximum falls behind
+    y = torch.zeros(1, vocab)
+    y[0, 3], y[0, 9] = 5.0, 4.0
+    seen = torch.tensor([3, 40], dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0, 2], dtype=torch.int32, device=DEV)
+    work = torch.empty(vocab, device=DEV)
+    assert _sorted_sample(y, [0.0], 1.0, top_k=1, repeat_penalty=2.0, seen=seen, seen_cu=cu, work=work) == [9]
+    # min_p above 1 empties the set: the reference answers with the argmax of the unpenalised logits
+    assert _sorted_sample(y, [0.5], 1.0, top_k=5, min_p=1.5, repeat_penalty=2.0, seen=seen, seen_cu=cu, work=work) == [3]
+    # the benchmark's vocabulary, peaked and flat rows
+    g = gen(77)
+    big = torch.randn(4, 151936, generator=g)
+    big[0] *= 6.0
+    us = [0.3, 0.77, 0.05, 0.999]
+    got = _sorted_sample(big, us, 0.8, top_k=40, top_p=0.9)
+    for r in range(4):
+        kind, pairs = P.target(big[r].tolist(), [], P.PlainSampleParams(temperature=0.8, top_k=40, top_p=0.9))
+        total = sum(w for _, w in pairs)
+        cum = 0.0
+        hit = False
+        for i, w in pairs:
+            lo, cum = cum, cum + w
+            if i == got[r]:
+                hit = lo - 1e-5 * total <= us[r] * total <= cum + 1e-5 * total
+        assert hit, (r, got[r])
+    # the same call twice: fixed-point masses make the answer independent of the order of the additions
+    assert got == _sorted_sample(big, us, 0.8, top_k=40, top_p=0.9)
+
+
 def test_sampling_penalties_and_min_p():
     vocab = 50
     x = torch.zeros(2, vocab)

@@ -198,7 +198,8 @@ KERNEL_SHAPES = {"qkv": (6144, 2560, 0), "o": (2560, 4096, 1), "gateup": (19456,
 def kernel_run(a) -> int:
     """Times ONE kernel on one workload (for profiling under ncu and for the files in profiles/):
     ``--kernel skinny_gemm|gemm_tcgen05 --shape qkv|o|gateup|down|head --rows M`` or
-    ``--kernel attention_decode|attention_prefill|attention_prefill_tcgen05 --rows B_or_T --ctx C``.  Weights rotate over
+    ``--kernel attention_decode|attention_prefill|attention_prefill_tcgen05 --rows B_or_T --ctx C``,
+    ``--kernel qk_norm_rope --rows T``.  Weights rotate over
     enough copies to exceed L2.  Prints one JSON line."""
     import torch
     from builderforce_inference_b200.kernels import fast_ops
@@ -218,6 +219,33 @@ def kernel_run(a) -> int:
                 raise SystemExit(f"{a.kernel} does not take M={m} N={n} K={k}")
         bytes_moved, flops = n * k * 2, 2.0 * m * n * k
         what = {"shape": a.shape, "M": m, "N": n, "K": k, "epilogue": epi}
+    elif a.kernel == "qk_norm_rope":
+        # q/k norm + rotation + cache write of one prompt of --rows tokens
+        from builderforce_inference_b200.cache import KVView
+        from builderforce_inference_b200.kernels import ops
+        from builderforce_inference_b200.parts.rotary import rotary_table
+        c = CONFIG_4B
+        nq, nkv, d = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"]
+        t = a.rows
+        blocks = (t + 63) // 64
+        table = torch.arange(blocks, dtype=torch.int32, device=dev).reshape(1, blocks)
+        copies = 4
+        kvs = [KVView(torch.zeros(blocks, nkv, 64, d, device=dev, dtype=torch.bfloat16),
+                      torch.zeros(blocks, nkv, 64, d, device=dev, dtype=torch.bfloat16), table, nkv, d, None)
+               for _ in range(copies)]
+        qkvs = [torch.randn(t, (nq + 2 * nkv) * d, device=dev, dtype=torch.bfloat16) for _ in range(copies)]
+        norm_w = torch.ones(d, device=dev, dtype=torch.bfloat16)
+        rope = rotary_table(c["rope_theta"], d, t, dev)
+        pos = torch.arange(t, dtype=torch.int32, device=dev)
+        slot = torch.zeros(t, dtype=torch.int32, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+        def one(i):
+            ops.qk_norm_rope_cache(qkvs[i % copies], nq, nkv, d, norm_w, norm_w, c["rms_norm_eps"], rope, d, pos, slot,
+                                   kvs[i % copies], ops.FLAG_WRITE_CACHE, status)
+        bytes_moved = t * (2 * nq + 3 * nkv) * d * 2          # q read and written, k and v read and written to the cache
+        flops = 0.0
+        what = {"tokens": t, "q_heads": nq, "kv_heads": nkv, "head_dim": d}
     else:
         from builderforce_inference_b200.cache import KVView
         c = CONFIG_4B
@@ -288,7 +316,7 @@ def kernel_run(a) -> int:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", default=None, choices=["skinny_gemm", "gemm_tcgen05", "attention_decode",
+    ap.add_argument("--kernel", default=None, choices=["skinny_gemm", "gemm_tcgen05", "qk_norm_rope", "attention_decode",
                                                        "attention_prefill", "attention_prefill_tcgen05"],
                     help="time one kernel instead of the model (see kernel_run)")
     ap.add_argument("--shape", default="qkv", choices=sorted(KERNEL_SHAPES))

@@ -327,28 +327,55 @@ qk_norm_rope_cache_vec_kernel(bf16* __restrict__ qkv, long token_stride, int n_t
     if (item >= (long)n_tokens * groups) return;
     const int t = (int)(item / groups);
     const int head_base = (int)(item - (long)t * groups) * HPW + lane / LANES;
-    const int slot = token_slot[t];
-    if (slot < 0) return;
-    const int pos = token_pos[t];
     bf16* row = qkv + (size_t)t * token_stride + sub * 8;
 
-    // every load of the warp's heads first, then the arithmetic
+    // every load of the warp's heads first (they need only the token's row), then its slot and position
     uint4 raw[QKV_UNROLL];
 #pragma unroll
     for (int u = 0; u < QKV_UNROLL; ++u) {
         const int hh = head_base + u * PER_WARP;
         raw[u] = hh < heads ? *reinterpret_cast<const uint4*>(row + (size_t)hh * D) : make_uint4(0u, 0u, 0u, 0u);
     }
+    const int slot = token_slot[t];
+    const int pos = token_pos[t];
+    if (slot < 0) return;
     const bool has_rope = rope_table != nullptr;
     const bool bad_pos = has_rope && (pos < 0 || pos >= table_positions);
+    // rotation factors and norm weights of this lane's 8 values, as whole 16-byte loads
     float2 cs[8];
     float wq[8], wk[8];
+    if (has_rope && !bad_pos) {
+        const float4* src = reinterpret_cast<const float4*>(rope_table + (size_t)pos * (D / 2) + (sub % (LANES / 2)) * 8);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        cs[j] = (has_rope && !bad_pos) ? rope_table[(size_t)pos * (D / 2) + (sub % (LANES / 2)) * 8 + j] : make_float2(1.0f, 0.0f);
-        wq[j] = q_norm_w ? load_as_f32(q_norm_w, norm_dtype, sub * 8 + j) : 1.0f;
-        wk[j] = k_norm_w ? load_as_f32(k_norm_w, norm_dtype, sub * 8 + j) : 1.0f;
+        for (int j = 0; j < 4; ++j) {
+            const float4 t4 = src[j];
+            cs[2 * j] = make_float2(t4.x, t4.y);
+            cs[2 * j + 1] = make_float2(t4.z, t4.w);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) cs[j] = make_float2(1.0f, 0.0f);
     }
+    auto load_w8 = [&](const void* w, float (&dst)[8]) {
+        if (w == nullptr) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) dst[j] = 1.0f;
+        } else if (norm_dtype == BFI_BF16 && ((uintptr_t)w & 15) == 0) {
+            const uint4 raw8 = reinterpret_cast<const uint4*>(w)[sub];
+            const uint32_t words[4] = {raw8.x, raw8.y, raw8.z, raw8.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __nv_bfloat162 two = *reinterpret_cast<const __nv_bfloat162*>(&words[j]);
+                dst[2 * j] = __low2float(two);
+                dst[2 * j + 1] = __high2float(two);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) dst[j] = load_as_f32(w, norm_dtype, sub * 8 + j);
+        }
+    };
+    load_w8(q_norm_w, wq);
+    load_w8(k_norm_w, wk);
     int page = 0;
     if (flags & 1) page = block_table[(size_t)slot * table_stride + pos / BFI_PAGE_TOKENS];
     if (bad_pos) {

@@ -176,3 +176,213 @@ def test_toy_architecture_with_state_repeated_layers_and_a_shared_cache():
         undo()
     from builderforce_inference_b200 import registered_architectures
     assert registered_architectures() == ["Qwen3ForCausalLM", "qwen3"]
+
+
+# ------------------------------------------------------------------------------------------------
+# A second unknown model: a feed-forward with routing (one of several experts per token, weighted
+# by the router's probability), a position encoding with code of its own (adjacent pairs instead
+# of rotate-half, so the attention kernels cannot fuse it), and a norm that subtracts the mean.
+# All three are defined here and registered as parts; nothing in the framework's files changes.
+# ------------------------------------------------------------------------------------------------
+R_WIDTH, R_HEADS, R_KV, R_D, R_INNER, R_EXPERTS, R_VOCAB, R_EPS, R_THETA = 40, 5, 1, 16, 24, 3, 61, 1e-6, 500.0
+ROUTED_CONFIG = {"architectures": ["ToyRoutedLM"], "model_type": "toy_routed", "vocab_size": R_VOCAB,
+                 "n_experts": R_EXPERTS, "max_position_embeddings": 128}
+
+
+def register_routed():
+    from builderforce_inference_b200 import Architecture, register_architecture, unregister_architecture
+    from builderforce_inference_b200.parts import (FEED_FORWARDS, NORMS, POSITION_ENCODINGS, FeedForward, LayerSpec, ModelSpec,
+                                                   Norm, ParamSpec, PartSpec, PositionEncoding, RunSpec)
+
+    class RoutedFeedForward(FeedForward):
+        """Top-1 routing: expert e = argmax(router h); x += p_e * down_e(silu(gate_e h) * up_e h)."""
+
+        def __init__(self, width, inner, n_experts):
+            self.width, self.inner, self.n_experts = width, inner, n_experts
+
+        def param_specs(self):
+            specs = {"router": ParamSpec((self.n_experts, self.width))}
+            for e in range(self.n_experts):
+                specs[f"experts.{e}.gate"] = ParamSpec((self.inner, self.width))
+                specs[f"experts.{e}.up"] = ParamSpec((self.inner, self.width))
+                specs[f"experts.{e}.down"] = ParamSpec((self.width, self.inner))
+            return specs
+
+        def load(self, tensors, runtime):
+            self.w = {k: v.float() for k, v in tensors.items()}
+
+        def forward(self, ctx, h, residual):
+            n = ctx.n_tokens
+            x = h[:n].float()
+            probs = torch.softmax(x @ self.w["router"].t(), dim=-1)           # router logits and softmax in float32
+            top_p, top_e = probs.max(dim=-1)
+            for e in range(self.n_experts):
+                rows = (top_e == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                xe = x[rows]
+                g, u = xe @ self.w[f"experts.{e}.gate"].t(), xe @ self.w[f"experts.{e}.up"].t()
+                y = (torch.nn.functional.silu(g) * u) @ self.w[f"experts.{e}.down"].t()
+                residual[rows] += top_p[rows, None] * y
+
+    class AdjacentPairRotary(PositionEncoding):
+        """Pairs (2i, 2i+1) turn by pos * theta^(-2i/d): not a rotate-half rotation, so it is applied
+        by its own code between the norms and the cache write."""
+
+        def __init__(self, theta, rot_dim):
+            self.theta, self.rot_dim = theta, rot_dim
+
+        def prepare(self, runtime, max_positions):
+            i = torch.arange(self.rot_dim // 2, dtype=torch.float64)
+            inv = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / self.rot_dim)
+            ang = torch.arange(max_positions, dtype=torch.float64)[:, None] * inv[None, :]
+            self.cos, self.sin = ang.cos().float().to(runtime.device), ang.sin().float().to(runtime.device)
+
+        def apply(self, ctx, q, k):
+            pos = ctx.token_pos[:ctx.n_tokens].long()
+            c, s = self.cos[pos][:, None, :], self.sin[pos][:, None, :]
+            for t in (q, k):
+                x = t[:ctx.n_tokens].float()
+                a, b = x[..., 0::2], x[..., 1::2]
+                out = torch.stack([a * c - b * s, a * s + b * c], dim=-1).reshape(x.shape)
+                t[:ctx.n_tokens] = out.to(t.dtype)
+
+    class CenteredNorm(Norm):
+        """y = (x - mean) * rsqrt(var + eps) * w."""
+
+        def __init__(self, width, eps):
+            self.width, self.eps = width, eps
+
+        def param_specs(self):
+            return {"weight": ParamSpec((self.width,), "norm")}
+
+        def load(self, tensors, runtime):
+            self.weight = tensors["weight"].float()
+
+        def forward(self, ctx, x, rows=None, tag="norm.out"):
+            src = x if rows is None else x[rows.long()]
+            out = ctx.rows(tag, self.width, n_rows=src.shape[0])
+            v = src.float()
+            v = v - v.mean(dim=-1, keepdim=True)
+            out.copy_((v * torch.rsqrt(v.pow(2).mean(dim=-1, keepdim=True) + self.eps) * self.weight).to(out.dtype))
+            return out
+
+    FEED_FORWARDS.register("routed_mlp", RoutedFeedForward)
+    POSITION_ENCODINGS.register("adjacent_rotary", AdjacentPairRotary)
+    NORMS.register("centered", CenteredNorm)
+
+    def describe(config):
+        rms = PartSpec("rms", {"width": R_WIDTH, "eps": R_EPS})
+        centered = PartSpec("centered", {"width": R_WIDTH, "eps": R_EPS})
+        att = PartSpec("attention", {"width": R_WIDTH, "n_heads": R_HEADS, "n_kv_heads": R_KV, "head_dim": R_D,
+                                     "position": PartSpec("adjacent_rotary", {"theta": R_THETA, "rot_dim": R_D})})
+        routed = PartSpec("routed_mlp", {"width": R_WIDTH, "inner": R_INNER, "n_experts": config["n_experts"]})
+        dense = PartSpec("gated_mlp", {"width": R_WIDTH, "inner": R_INNER})
+
+        def layer(i, norm, ffn, ffn_names):
+            names = {"norm1.weight": f"l{i}.n1", "norm2.weight": f"l{i}.n2"}
+            names.update({f"mixer.{k}": f"l{i}.att.{k}" for k in ("q_proj", "k_proj", "v_proj", "o_proj")})
+            names.update({f"ffn.{k}": f"l{i}.ffn.{k}" for k in ffn_names})
+            return LayerSpec(PartSpec("prenorm", {"norm1": norm, "mixer": att, "norm2": norm, "ffn": ffn}), names)
+
+        routed_names = ["router"] + [f"experts.{e}.{m}" for e in range(config["n_experts"]) for m in ("gate", "up", "down")]
+        layers = (layer(0, centered, routed, routed_names), layer(1, rms, dense, ["gate_proj", "up_proj", "down_proj"]))
+        return ModelSpec(vocab_size=config["vocab_size"], width=R_WIDTH, embedding_name="emb", layers=layers,
+                         schedule=(RunSpec(0), RunSpec(1)), final_norm=centered, final_norm_names={"weight": "out_norm"},
+                         head_name="head", max_positions=config["max_position_embeddings"])
+
+    register_architecture(("toy_routed", "ToyRoutedLM"), Architecture("toy_routed", dict, describe))
+
+    def undo():
+        unregister_architecture("toy_routed", "ToyRoutedLM")
+        FEED_FORWARDS.unregister("routed_mlp")
+        POSITION_ENCODINGS.unregister("adjacent_rotary")
+        NORMS.unregister("centered")
+    return undo
+
+
+ROUTED_TO = set()
+
+
+def plain_routed(w, tokens):
+    t = len(tokens)
+    x = P.embedding(w["emb"], tokens)
+
+    def centered(v, weight):
+        v = v - v.mean(dim=-1, keepdim=True)
+        return v * torch.rsqrt(v.pow(2).mean(dim=-1, keepdim=True) + R_EPS) * weight
+
+    def adjacent(v):                                     # [t, heads, d]
+        i = torch.arange(R_D // 2, dtype=torch.float64)
+        ang = torch.arange(t, dtype=torch.float64)[:, None] * torch.pow(torch.tensor(R_THETA, dtype=torch.float64), -2.0 * i / R_D)
+        c, s = ang.cos().float()[:, None, :], ang.sin().float()[:, None, :]
+        a, b = v[..., 0::2], v[..., 1::2]
+        return torch.stack([a * c - b * s, a * s + b * c], dim=-1).reshape(v.shape)
+
+    def attend(x, i, norm):
+        h = norm(x, w[f"l{i}.n1"])
+        q = adjacent(P.linear(w[f"l{i}.att.q_proj"], h).reshape(t, R_HEADS, R_D))
+        k = adjacent(P.linear(w[f"l{i}.att.k_proj"], h).reshape(t, R_KV, R_D))
+        v = P.linear(w[f"l{i}.att.v_proj"], h).reshape(t, R_KV, R_D)
+        return x + P.linear(w[f"l{i}.att.o_proj"], P.attention(q, k, v).reshape(t, R_HEADS * R_D))
+
+    x = attend(x, 0, centered)
+    h = centered(x, w["l0.n2"])
+    probs = torch.softmax(P.linear(w["l0.ffn.router"], h), dim=-1)
+    rows = []
+    for r in range(t):
+        e = int(probs[r].argmax())
+        ROUTED_TO.add(e)
+        hr = h[r:r + 1]
+        y = P.linear(w[f"l0.ffn.experts.{e}.down"], P.swiglu(P.linear(w[f"l0.ffn.experts.{e}.gate"], hr),
+                                                              P.linear(w[f"l0.ffn.experts.{e}.up"], hr)))
+        rows.append(probs[r, e] * y)
+    x = x + torch.cat(rows)
+    rms = lambda v, weight: P.rms_norm(v, weight, R_EPS)
+    x = attend(x, 1, rms)
+    h = rms(x, w["l1.n2"])
+    x = x + P.linear(w["l1.ffn.down_proj"], P.swiglu(P.linear(w["l1.ffn.gate_proj"], h), P.linear(w["l1.ffn.up_proj"], h)))
+    return P.linear(w["head"], centered(x, w["out_norm"]))
+
+
+def test_toy_architecture_with_routing_another_position_encoding_and_another_norm():
+    from builderforce_inference_b200 import write_model_folder
+    from builderforce_inference_b200.engine.engine import Engine, SequenceStep as S
+    undo = register_routed()
+    try:
+        folder = tempfile.mkdtemp(prefix="bfi_toy_routed_")
+        write_model_folder(ROUTED_CONFIG, 5, folder, torch.float32)
+        w = {k: v.float() for k, v in P.read_safetensors(os.path.join(folder, "model.safetensors")).items()}
+        assert "l0.ffn.experts.2.down" in w and "l1.ffn.gate_proj" in w
+        eng = Engine.load(folder, dtype="float32", max_tokens=512)
+        assert not eng.use_graphs                      # the toy parts are not graph-safe
+        g = torch.Generator().manual_seed(2)
+        prompts = [torch.randint(0, R_VOCAB, (n,), generator=g).tolist() for n in (66, 7, 21)]
+        refs = [plain_routed(w, p) for p in prompts]
+        assert len(ROUTED_TO) >= 2, "the prompts must reach more than one expert, or the routing is not tested"
+        for p, r in zip(prompts, refs):
+            s = eng.acquire()
+            assert rel_err(eng.step([S(s, p, list(range(len(p))))]).cpu(), r) < 1e-4
+            eng.release(s)
+        # unequal batch, then token by token
+        slots = [eng.acquire() for _ in prompts]
+        pre = [50, 3, 20]
+        lg = eng.step([S(s, p[:k], [k - 1]) for s, p, k in zip(slots, prompts, pre)]).cpu().clone()
+        for i, k in enumerate(pre):
+            assert rel_err(lg[i:i + 1], refs[i][k - 1:k]) < 1e-4
+        pos = list(pre)
+        live = [0, 1, 2]
+        while live:
+            lg = eng.step([S(slots[i], [prompts[i][pos[i]]], [0]) for i in live]).cpu().clone()
+            for j, i in enumerate(live):
+                assert rel_err(lg[j:j + 1], refs[i][pos[i]:pos[i] + 1]) < 1e-4, (i, pos[i])
+                pos[i] += 1
+            for i in list(live):
+                if pos[i] == len(prompts[i]):
+                    eng.release(slots[i])
+                    live.remove(i)
+        eng.cache.check()
+    finally:
+        undo()
+    from builderforce_inference_b200 import registered_architectures
+    assert registered_architectures() == ["Qwen3ForCausalLM", "qwen3"]

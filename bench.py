@@ -33,6 +33,13 @@ CONFIG_4B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hid
                  num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=9728,
                  vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True,
                  max_position_embeddings=40960)
+# the other shapes of the same architecture, for runs beside the benchmark (``--model``)
+SHAPES = {
+    "4b": CONFIG_4B,
+    "8b": dict(CONFIG_4B, hidden_size=4096, intermediate_size=12288, tie_word_embeddings=False),
+    "32b": dict(CONFIG_4B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600,
+                tie_word_embeddings=False),
+}
 FULL_LAYERS = 36
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
@@ -163,7 +170,7 @@ def e2e_run(model, batch, steps, warmup, seed):
     return {"tok_s": tokens / (t1 - t0), "h2d": model.stepper.h2d_bytes, "d2h": model.stepper.d2h_bytes}
 
 
-def prefill_run(model, tokens, reps, layers):
+def prefill_run(model, tokens, reps, layers, c=None):
     import torch
     from builderforce_inference_b200.engine.engine import SequenceStep
     eng = model.engine
@@ -182,7 +189,7 @@ def prefill_run(model, tokens, reps, layers):
             times.append(e0.elapsed_time(e1))
         eng.release(s)
     ms = statistics.median(times)
-    c = CONFIG_4B
+    c = c or CONFIG_4B
     h, d, nq, nkv, inter = c["hidden_size"], c["head_dim"], c["num_attention_heads"], c["num_key_value_heads"], \
         c["intermediate_size"]
     per_layer = 2 * tokens * (h * (nq + 2 * nkv) * d + nq * d * h + 3 * h * inter)
@@ -327,7 +334,9 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="run fewer layers of the same sizes")
+    ap.add_argument("--model", dest="shape_name", default="4b", choices=sorted(SHAPES),
+                    help="layer sizes: the benchmark's Qwen3-4B shape, or the 8B / 32B shapes for runs beside it")
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers of the same sizes")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     a = ap.parse_args()
@@ -346,7 +355,11 @@ def main() -> int:
     import torch
     from builderforce_inference_b200 import Model
     pk = peaks()
-    cfg = dict(CONFIG_4B, num_hidden_layers=a.layers)
+    shape_cfg = SHAPES[a.shape_name]
+    full_layers = shape_cfg["num_hidden_layers"]
+    if a.layers is None:
+        a.layers = full_layers
+    cfg = dict(shape_cfg, num_hidden_layers=a.layers)
     max_batch = a.batch if a.no_points else max(64, a.batch)
     t_load = time.time()
     model = Model.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=max_batch * CONTEXT, max_seq_len=CONTEXT,
@@ -367,22 +380,22 @@ def main() -> int:
                 continue
             decode_run(model, b, 2, 3, seed=3)
             points[f"decode_b{b}"] = round(decode_run(model, b, min(a.steps, 32), warmup, seed=4)["tok_s"], 1)
-        pf = prefill_run(model, PREFILL_TOKENS, 5, a.layers)
+        pf = prefill_run(model, PREFILL_TOKENS, 5, a.layers, shape_cfg)
         prefill = {"value": round(pf["tok_s"], 1), "tokens": PREFILL_TOKENS, "ms": round(pf["ms"], 3),
                    "frac": round(pf["flops"] / (pf["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
     clk = clocks.stop()
 
     achieved = main_run["step_bytes"] / (main_run["ms_per_step"] / 1e3) / 1e9
-    c = CONFIG_4B
+    c = shape_cfg
     line = {
-        "metric": "Qwen3-4B bf16 decode tok/s at batch 8 (batch 1/64 in points; prefill tok/s at 2,048 tokens)",
+        "metric": f"Qwen3-{a.shape_name.upper()} bf16 decode tok/s at batch {a.batch} (batch 1/64 in points; prefill tok/s at 2,048 tokens)",
         "value": round(main_run["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": warmup,
         "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random weights",
-        "config": {"model": "qwen3-4b-shape", "layers": a.layers, "layers_full": FULL_LAYERS,
+        "config": {"model": f"qwen3-{a.shape_name}-shape", "layers": a.layers, "layers_full": full_layers,
                    "hidden": c["hidden_size"], "q_heads": c["num_attention_heads"],
                    "kv_heads": c["num_key_value_heads"], "head_dim": c["head_dim"],
-                   "intermediate": c["intermediate_size"], "vocab": c["vocab_size"], "tied_head": True,
+                   "intermediate": c["intermediate_size"], "vocab": c["vocab_size"], "tied_head": bool(c["tie_word_embeddings"]),
                    "global_batch": a.batch, "seq_len": CONTEXT, "prompt_len": "uniform[128,2048]",
                    "ctx_mean": round(main_run["ctx_mean"], 1), "parallelism": "single-gpu",
                    "l2": "weights read per step exceed L2", "peaks": pk["source"]},

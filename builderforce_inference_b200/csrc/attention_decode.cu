@@ -28,8 +28,8 @@ attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
                         const int* __restrict__ seq_start, int n_q, int n_kv, int window, float scale_log2,
                         int head_chunks, float* __restrict__ part_o, float* __restrict__ part_ml,
                         int* __restrict__ counters) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* ks[2] = {reinterpret_cast<bf16*>(smem_raw), reinterpret_cast<bf16*>(smem_raw) + 2 * AD_TILE * D};
     bf16* vs[2] = {ks[0] + AD_TILE * D, ks[1] + AD_TILE * D};
@@ -294,8 +294,8 @@ template <int D>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                                               bf16* __restrict__ out, long out_stride, int n_q, int max_splits, int window) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const int seq = blockIdx.y, head = blockIdx.x;
     if (seq_slot[seq] < 0) return;
     const int pos = seq_start[seq];

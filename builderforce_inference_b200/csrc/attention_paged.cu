@@ -26,8 +26,8 @@ attention_paged_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
                        const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_seqlens,
                        const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int n_q, int n_kv, int d,
                        int gh, int head_chunks, int window, float scale) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     extern __shared__ float smem[];
     float* qs = smem;                          // [ATT_ROWS][d]
     float* ks = qs + ATT_ROWS * d;             // [ATT_KEYS][d + 1]

@@ -20,8 +20,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, long q_stride, bf16* __rest
                          const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_seqlens,
                          const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int n_q, int n_kv,
                          int window, float scale_log2) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* qs = reinterpret_cast<bf16*>(smem_raw);                       // [64][D]
     bf16* ks[2] = {qs + AP_QROWS * D, qs + AP_QROWS * D + 2 * AD_TILE * D};

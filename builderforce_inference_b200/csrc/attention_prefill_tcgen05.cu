@@ -168,8 +168,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
 
     if (warp == 4) {
         // ---------------------------------------------------------------- TMA producer

@@ -16,8 +16,8 @@
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                   float* __restrict__ out, int width, int vocab, int* status) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * width;
@@ -52,8 +52,8 @@ template <typename TX>
 __global__ void rmsnorm_kernel(const TX* __restrict__ x, long x_stride, const int* __restrict__ rows,
                                const void* __restrict__ w, int w_dtype, void* __restrict__ out,
                                int out_dtype, long out_stride, int width, float eps) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const long src = rows ? (long)rows[r] : (long)r;
@@ -79,8 +79,8 @@ __global__ void __launch_bounds__(256)
 rmsnorm_regs_kernel(const float* __restrict__ x, long x_stride, const int* __restrict__ rows,
                     const void* __restrict__ w, int w_dtype, void* __restrict__ out, int out_dtype,
                     long out_stride, int width, float eps) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const long src = rows ? (long)rows[r] : (long)r;
@@ -171,8 +171,8 @@ __device__ __forceinline__ float silu_f32(float g) {
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, long in_stride, T* __restrict__ out, long out_stride,
                                 int n_rows, int inter, int interleaved) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const long total = (long)n_rows * inter;
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
         const long r = i / inter;
@@ -223,8 +223,8 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, long token_stride
                                           const int* __restrict__ token_slot, T* __restrict__ k_pages,
                                           T* __restrict__ v_pages, const int* __restrict__ block_table,
                                           int table_stride, int flags, int* status) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     __shared__ float buf[QKR_WARPS][QKR_MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = n_q + 2 * n_kv;
@@ -315,8 +315,8 @@ qk_norm_rope_cache_vec_kernel(bf16* __restrict__ qkv, long token_stride, int n_t
                               const int* __restrict__ token_pos, const int* __restrict__ token_slot,
                               bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, const int* __restrict__ block_table,
                               int table_stride, int flags, int* status) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     constexpr int LANES = D / 8;                        // a lane owns 8 consecutive values (16 bytes)
     constexpr int PER_WARP = 32 / LANES;
     constexpr int HPW = PER_WARP * QKV_UNROLL;          // consecutive heads of one token per warp
@@ -501,8 +501,8 @@ extern "C" int bfi_qk_norm_rope_cache(void* qkv, int dtype, long token_stride, i
 // out[i] += add[i]  (float32 residual stream += an activation)
 template <typename T>
 __global__ void residual_add_kernel(float* __restrict__ x, const T* __restrict__ y, long n) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x)
         x[i] += to_f32(y[i]);
 }

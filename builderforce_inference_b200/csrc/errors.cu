@@ -23,7 +23,7 @@ int bfi_check_launch(const char* what) {
 }
 
 // Off unless asked for: measured on the decode step, early launch of dependents did not pay.
-int g_bfi_pdl = 0;
+int g_bfi_pdl = 1;
 
 // Turns programmatic dependent launch on (1) or off (0) for every later launch of this library.
 extern "C" int bfi_set_pdl(int on) {

@@ -38,8 +38,8 @@ template <typename TA, typename TW>
 __global__ void __launch_bounds__(256)
 gemm_tile_kernel(const TA* __restrict__ A, long lda, const TW* __restrict__ W, long ldw, void* __restrict__ C,
                  int c_dtype, long ldc, int M, int N, int K, int epilogue) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     __shared__ __align__(16) float As[TK][TM + TPAD];
     __shared__ __align__(16) float Ws[TK][TN + TPAD];
     const int tid = threadIdx.x;
@@ -121,8 +121,8 @@ template <typename TA, typename TW, int MB>
 __global__ void __launch_bounds__(256)
 gemv_rows_kernel(const TA* __restrict__ A, long lda, const TW* __restrict__ W, long ldw, void* __restrict__ C,
                  int c_dtype, long ldc, int m_base, int M, int N, int K, int epilogue) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int pair = blockIdx.x * (blockDim.x >> 5) + warp;
     const int n_a = pair * 2, n_b = n_a + 1;

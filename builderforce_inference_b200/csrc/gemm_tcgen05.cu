@@ -92,16 +92,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    pdl_wait();
-    pdl_trigger();
 
     if (warp == 0) {
         // ---------------- TMA producer
         if (lane == 0) {
-            for (int i = 0; i < n_kb; ++i) {
+            // W does not depend on the kernel before this one: the ring fills with W tiles before the
+            // wait for that kernel (programmatic dependent launch), the A tiles follow after it
+            const int early = n_kb < Cfg::STAGES ? n_kb : Cfg::STAGES;
+            pdl_trigger();
+            for (int i = 0; i < early; ++i) {
+                mbar_expect_tx(&full[i], Cfg::STAGE_BYTES);
+                tma_load_2d(smem + (size_t)i * Cfg::STAGE_BYTES, &map_w, (kb_beg + i) * TC_BK, n0, &full[i]);
+            }
+            pdl_wait();
+            for (int i = 0; i < early; ++i)
+                tma_load_2d(smem + (size_t)i * Cfg::STAGE_BYTES + TC_ROWS * TC_BK * 2, &map_a, (kb_beg + i) * TC_BK, m0, &full[i]);
+            for (int i = early; i < n_kb; ++i) {
                 const int s = i % Cfg::STAGES;
                 const uint32_t phase = (i / Cfg::STAGES) & 1;
-                if (i >= Cfg::STAGES && !mbar_wait(&empty[s], phase ^ 1)) {
+                if (!mbar_wait(&empty[s], phase ^ 1)) {
                     atomicOr(status, BFI_STATUS_TIMEOUT);
                     s_flag[0] = 1;
                     break;
@@ -112,6 +121,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 tma_load_2d(stage, &map_w, k, n0, &full[s]);
                 tma_load_2d(stage + TC_ROWS * TC_BK * 2, &map_a, k, m0, &full[s]);
             }
+        } else {
+            pdl_trigger();
+            pdl_wait();
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer
@@ -140,6 +152,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
     } else {
         // ---------------- epilogue warps: TMEM lanes 32*(warp % 4) .. +31
+        pdl_trigger();
+        pdl_wait();                                      // C may still be in use by the kernel before
         const int quad = warp & 3;
         const int n_local = quad * 32 + lane;
         const int n = n0 + n_local;
@@ -317,8 +331,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    pdl_wait();
-    pdl_trigger();
+    pdl_trigger();                                 // the kernel after this one may start its own preamble
 
     // tiles in bands of 8 token tiles: blocks that run together share W tiles and A tiles in L2
     auto tile_coords = [&](int tile, int& tm, int& tn) {
@@ -333,10 +346,27 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     if (warp == 0) {
         if (lane == 0) {
             int it = 0;                                            // k blocks issued so far, over all tiles
+            bool first = true;
             for (int tile = blockIdx.x; tile < n_tiles && !s_flag[0]; tile += gridDim.x) {
                 int tm, tn;
                 tile_coords(tile, tm, tn);
-                for (int i = 0; i < n_kb; ++i, ++it) {
+                int i0 = 0;
+                if (first) {
+                    // W does not depend on the kernel before this one: the first stages' W halves travel
+                    // before the wait for that kernel, their A halves after it
+                    const int early = n_kb < n_stages ? n_kb : n_stages;
+                    for (int i = 0; i < early; ++i) {
+                        mbar_expect_tx(&full[i], stage_bytes);
+                        tma_load_2d(smem + (size_t)i * stage_bytes + TILE_TOKENS * TC_BK * 2, &map_w, i * TC_BK, tn * tile_n,
+                                    &full[i]);
+                    }
+                    pdl_wait();
+                    for (int i = 0; i < early; ++i)
+                        tma_load_2d(smem + (size_t)i * stage_bytes, &map_a, i * TC_BK, tm * TILE_TOKENS, &full[i]);
+                    it = i0 = early;
+                    first = false;
+                }
+                for (int i = i0; i < n_kb; ++i, ++it) {
                     const int s = it % n_stages;
                     const uint32_t phase = (it / n_stages) & 1;
                     if (it >= n_stages && !mbar_wait(&empty[s], phase ^ 1)) {
@@ -350,6 +380,9 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                     tma_load_2d(stage + TILE_TOKENS * TC_BK * 2, &map_w, i * TC_BK, tn * tile_n, &full[s]);
                 }
             }
+            if (first) pdl_wait();
+        } else {
+            pdl_wait();
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -401,6 +434,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             }
         }
     } else {
+        pdl_wait();                                      // C may still be in use by the kernel before
         const int quad = warp & 3;
         int local = 0;
         bool alive = true;

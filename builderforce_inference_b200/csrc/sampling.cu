@@ -77,8 +77,8 @@ sample_rows_kernel(const float* __restrict__ logits, long stride, float* __restr
                    const int* __restrict__ seen, const int* __restrict__ seen_cu, const float* __restrict__ temperature,
                    const float* __restrict__ u_draw, float repeat_penalty, float presence_penalty, float min_p,
                    int* __restrict__ out) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     __shared__ ArgBest abest[33];
     __shared__ float fscratch[33];
     __shared__ float warp_tot[32];
@@ -355,8 +355,8 @@ sample_sorted_rows_kernel(const float* __restrict__ logits, long stride, float* 
                           int vocab, const int* __restrict__ seen, const int* __restrict__ seen_cu,
                           const float* __restrict__ temperature, const float* __restrict__ u_draw, float repeat_penalty,
                           float presence_penalty, int top_k, float top_p, float min_p, int* __restrict__ out) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     __shared__ ArgBest abest[33];
     __shared__ float fscratch[33];
     __shared__ int h_cnt[256];
@@ -527,8 +527,8 @@ extern "C" int bfi_sample_sorted_rows(const float* logits, long stride, float* w
 // Greedy only: out[row] = lowest index of the row maximum.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_rows_kernel(const float* __restrict__ logits, long stride, int vocab, int* __restrict__ out) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     __shared__ ArgBest abest[33];
     const float* x = logits + (size_t)blockIdx.x * stride;
     ArgBest mine;
@@ -552,8 +552,8 @@ argmax_rows_kernel(const float* __restrict__ logits, long stride, int vocab, int
 __global__ void __launch_bounds__(256)
 argmax_chunks_kernel(const float* __restrict__ logits, long stride, int vocab, int n_chunks, float* __restrict__ best_v,
                      int* __restrict__ best_i) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     __shared__ ArgBest abest[33];
     const int row = blockIdx.y, chunk = blockIdx.x;
     const float* x = logits + (size_t)row * stride;
@@ -577,8 +577,8 @@ argmax_chunks_kernel(const float* __restrict__ logits, long stride, int vocab, i
 
 __global__ void __launch_bounds__(64)
 argmax_pick_kernel(const float* __restrict__ best_v, const int* __restrict__ best_i, int n_chunks, int* __restrict__ out) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     __shared__ ArgBest abest[33];
     const int row = blockIdx.x;
     ArgBest mine;

@@ -140,8 +140,8 @@ __global__ void skinny_gemm_kernel(const bf16* __restrict__ A, long lda, const b
             }
         }
     }
+    pdl_trigger();
     pdl_wait();
-    pdl_trigger();       // only now: at most one later kernel sits waiting on the SMs
     for (int k0 = kbeg; k0 < kend; k0 += 32 * U) {
         if (k0 != kbeg) {
             SKINNY_LOAD(k0)

@@ -113,18 +113,13 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: 
         _ptr(tc_status(a.device)), _stream())
 
 
-TCGEN05_MIN_ROWS = 9             # fewer rows: the register-fed weight streamer ...
-TCGEN05_MIN_WEIGHTS = 20_000_000   # ... unless the matrix is large: then the TMA ring streams it faster at any row count
-
-
 def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int) -> bool:
-    """bfloat16 x bfloat16 -> ``out`` (float32 or bfloat16): the weight streamer for very few rows
-    of a small matrix, the tcgen05 kernel otherwise; False if neither takes the shape."""
-    m = a.shape[0]
-    tc_first = m >= TCGEN05_MIN_ROWS or w.shape[0] * w.shape[1] >= TCGEN05_MIN_WEIGHTS
-    if tc_first and gemm_tcgen05(a, w, out, epilogue):
+    """bfloat16 x bfloat16 -> ``out`` (float32 or bfloat16): the tcgen05 kernel, whose blocks start
+    streaming W into their shared memory while the kernel before them still runs; the register-fed
+    weight streamer for the shapes TMA cannot address; False if neither takes the shape."""
+    if gemm_tcgen05(a, w, out, epilogue):
         return True
-    if m <= SKINNY_MAX_ROWS:
+    if a.shape[0] <= SKINNY_MAX_ROWS:
         return skinny_gemm(a, w, out, epilogue)
     return False
 

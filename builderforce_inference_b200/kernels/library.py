@@ -35,10 +35,10 @@ class KernelLibrary:
         self.lib.bfi_last_error.restype = ctypes.c_char_p
         self._funcs: Dict[str, ctypes._CFuncPtr] = {}
         self.calls = 0          # exported functions called so far (each launches at least one kernel)
-        # BFI_B200_PDL=1 turns programmatic dependent launch on (a kernel may then start, and
-        # prefetch weights, while its predecessor drains)
-        if os.environ.get("BFI_B200_PDL", "0") == "1":
-            self.lib.bfi_set_pdl(ctypes.c_int(1))
+        # Programmatic dependent launch is on: a kernel may start, and stream weights into its
+        # shared memory, while its predecessor still runs.  BFI_B200_PDL=0 turns it off.
+        if os.environ.get("BFI_B200_PDL", "1") == "0":
+            self.lib.bfi_set_pdl(ctypes.c_int(0))
 
     def call_optional(self, func: str, *args) -> bool:
         """For kernels that may decline a shape: True if it ran, False if it declined (code 2)."""

@@ -29,7 +29,6 @@ attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
                         int head_chunks, float* __restrict__ part_o, float* __restrict__ part_ml,
                         int* __restrict__ counters) {
     pdl_trigger();
-    pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* ks[2] = {reinterpret_cast<bf16*>(smem_raw), reinterpret_cast<bf16*>(smem_raw) + 2 * AD_TILE * D};
     bf16* vs[2] = {ks[0] + AD_TILE * D, ks[1] + AD_TILE * D};
@@ -56,6 +55,27 @@ attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
     const int p_beg = first_page + split * pages_per_split;
     const int p_end = min(last_page + 1, p_beg + pages_per_split);
 
+    const size_t page_elems = (size_t)n_kv * AD_TILE * D;
+    const int* table = block_table + (size_t)slot * table_stride;
+
+    auto issue = [&](int page_idx, int stage) {
+        const int page = table[page_idx];
+        if (page >= 0) {
+            const size_t base = (size_t)page * page_elems + (size_t)kvh * AD_TILE * D;
+            load_tile<D>(ks[stage], k_pages + base);
+            load_tile<D>(vs[stage], v_pages + base);
+        }
+        cp_async_commit();
+    };
+
+    // The sequence's older pages, its slot, position and page table were all written before this
+    // step's kernels began; only the page of the new token (the last one) and q come from the
+    // kernel before this one.  So the first tile, unless it is that page, travels before the wait.
+    const bool early_tile = p_beg < p_end && p_beg != last_page;
+    if (early_tile) issue(p_beg, 0);
+    pdl_wait();
+    if (p_beg < p_end && !early_tile) issue(p_beg, 0);
+
     // query fragments: rows g and g+8 are heads head0+g, head0+g+8
     const bf16* qbase = q + (size_t)seq * q_stride;       // one token per sequence: row index = seq
     uint32_t qa[D / 16][4];
@@ -81,20 +101,6 @@ attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
 #pragma unroll
         for (int j = 0; j < 4; ++j) o[i][j] = 0.0f;
 
-    const size_t page_elems = (size_t)n_kv * AD_TILE * D;
-    const int* table = block_table + (size_t)slot * table_stride;
-
-    auto issue = [&](int page_idx, int stage) {
-        const int page = table[page_idx];
-        if (page >= 0) {
-            const size_t base = (size_t)page * page_elems + (size_t)kvh * AD_TILE * D;
-            load_tile<D>(ks[stage], k_pages + base);
-            load_tile<D>(vs[stage], v_pages + base);
-        }
-        cp_async_commit();
-    };
-
-    if (p_beg < p_end) issue(p_beg, 0);
     for (int p = p_beg; p < p_end; ++p) {
         const int stage = (p - p_beg) & 1;
         if (p + 1 < p_end) {

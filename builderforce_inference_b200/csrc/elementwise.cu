@@ -80,12 +80,22 @@ rmsnorm_regs_kernel(const float* __restrict__ x, long x_stride, const int* __res
                     const void* __restrict__ w, int w_dtype, void* __restrict__ out, int out_dtype,
                     long out_stride, int width, float eps) {
     pdl_trigger();
-    pdl_wait();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
-    const long src = rows ? (long)rows[r] : (long)r;
-    const float4* xr = reinterpret_cast<const float4*>(x + src * x_stride);
     const int n4 = width >> 2;
+    // the weights and the row index do not come from the kernel before this one: fetched before the wait
+    const long src = rows ? (long)rows[r] : (long)r;
+    float4 wv[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int j = i * 256 + threadIdx.x;
+        const int c = j * 4;
+        wv[i] = j < n4 ? make_float4(load_as_f32(w, w_dtype, c), load_as_f32(w, w_dtype, c + 1), load_as_f32(w, w_dtype, c + 2),
+                                     load_as_f32(w, w_dtype, c + 3))
+                       : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    pdl_wait();
+    const float4* xr = reinterpret_cast<const float4*>(x + src * x_stride);
     float4 v[VPT];
     float ss = 0.0f;
 #pragma unroll
@@ -105,10 +115,10 @@ rmsnorm_regs_kernel(const float* __restrict__ x, long x_stride, const int* __res
         const int j = i * 256 + threadIdx.x;
         if (j >= n4) continue;
         const int c = j * 4;
-        const float o0 = v[i].x * scale * load_as_f32(w, w_dtype, c);
-        const float o1 = v[i].y * scale * load_as_f32(w, w_dtype, c + 1);
-        const float o2 = v[i].z * scale * load_as_f32(w, w_dtype, c + 2);
-        const float o3 = v[i].w * scale * load_as_f32(w, w_dtype, c + 3);
+        const float o0 = v[i].x * scale * wv[i].x;
+        const float o1 = v[i].y * scale * wv[i].y;
+        const float o2 = v[i].z * scale * wv[i].z;
+        const float o3 = v[i].w * scale * wv[i].w;
         if (out_dtype == BFI_F32) {
             *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + obase + c) = make_float4(o0, o1, o2, o3);
         } else {
@@ -316,7 +326,6 @@ qk_norm_rope_cache_vec_kernel(bf16* __restrict__ qkv, long token_stride, int n_t
                               bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, const int* __restrict__ block_table,
                               int table_stride, int flags, int* status) {
     pdl_trigger();
-    pdl_wait();
     constexpr int LANES = D / 8;                        // a lane owns 8 consecutive values (16 bytes)
     constexpr int PER_WARP = 32 / LANES;
     constexpr int HPW = PER_WARP * QKV_UNROLL;          // consecutive heads of one token per warp
@@ -329,13 +338,6 @@ qk_norm_rope_cache_vec_kernel(bf16* __restrict__ qkv, long token_stride, int n_t
     const int head_base = (int)(item - (long)t * groups) * HPW + lane / LANES;
     bf16* row = qkv + (size_t)t * token_stride + sub * 8;
 
-    // every load of the warp's heads first (they need only the token's row), then its slot and position
-    uint4 raw[QKV_UNROLL];
-#pragma unroll
-    for (int u = 0; u < QKV_UNROLL; ++u) {
-        const int hh = head_base + u * PER_WARP;
-        raw[u] = hh < heads ? *reinterpret_cast<const uint4*>(row + (size_t)hh * D) : make_uint4(0u, 0u, 0u, 0u);
-    }
     const int slot = token_slot[t];
     const int pos = token_pos[t];
     if (slot < 0) return;
@@ -378,6 +380,15 @@ qk_norm_rope_cache_vec_kernel(bf16* __restrict__ qkv, long token_stride, int n_t
     load_w8(k_norm_w, wk);
     int page = 0;
     if (flags & 1) page = block_table[(size_t)slot * table_stride + pos / BFI_PAGE_TOKENS];
+    // the token's slot, position, page, rotation factors and the norm weights were all there before this
+    // step's kernels began; only the heads themselves come from the kernel before this one
+    pdl_wait();
+    uint4 raw[QKV_UNROLL];
+#pragma unroll
+    for (int u = 0; u < QKV_UNROLL; ++u) {
+        const int hh = head_base + u * PER_WARP;
+        raw[u] = hh < heads ? *reinterpret_cast<const uint4*>(row + (size_t)hh * D) : make_uint4(0u, 0u, 0u, 0u);
+    }
     if (bad_pos) {
         if (lane == 0 && status) atomicOr(status, BFI_STATUS_BAD_POSITION);
         return;

@@ -4,8 +4,8 @@
 // pages of 64 keys through a two-stage cp.async ring in shared memory, all query heads of the
 // group share the loaded keys and values (they are the 16 rows of the tensor-core tiles), and
 // partial results (running maximum, sum and unnormalised output, float32) go to a scratch buffer.
-// They are merged in range order: by the last block of a (sequence, kv head) to finish (a counter,
-// no waiting) when the batch is small, by a second kernel otherwise.
+// They are merged in range order by a second kernel (which, launched as a programmatic dependent,
+// is already resident when the first one ends).
 //
 // Scores, the running maximum and sum, and the output accumulator are float32; exp is
 // ex2.approx on scores pre-multiplied by log2(e).
@@ -19,15 +19,13 @@ __device__ __forceinline__ int decode_pages_per_split(int n_pages, int max_split
 
 // part_o  [seqs, n_q, max_splits, D]  float32 unnormalised outputs
 // part_ml [seqs, n_q, max_splits, 2]  float32 (running max in log2 units, running sum)
-// counters [seqs, gridDim.y] int32, zero before the launch and zero again after it
 template <int D>
 __global__ void __launch_bounds__(AD_THREADS)
 attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out, long out_stride,
                         const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                         const int* __restrict__ block_table, int table_stride, const int* __restrict__ seq_slot,
                         const int* __restrict__ seq_start, int n_q, int n_kv, int window, float scale_log2,
-                        int head_chunks, float* __restrict__ part_o, float* __restrict__ part_ml,
-                        int* __restrict__ counters) {
+                        int head_chunks, float* __restrict__ part_o, float* __restrict__ part_ml) {
     pdl_trigger();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* ks[2] = {reinterpret_cast<bf16*>(smem_raw), reinterpret_cast<bf16*>(smem_raw) + 2 * AD_TILE * D};
@@ -245,57 +243,9 @@ attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
             }
         }
     }
-    if (n_splits == 1 || counters == nullptr) return;     // without counters a second kernel merges
-
-    // ---- the last range of this (sequence, kv head) to arrive merges them all, in range order
-    __shared__ int s_last;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int* counter = counters + (size_t)seq * gridDim.y + blockIdx.y;
-        const int ticket = atomicAdd(counter, 1);
-        s_last = ticket == n_splits - 1;
-        if (s_last) *counter = 0;
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    // weights of the ranges first (one thread per head and range), so that the sums below are
-    // independent loads the memory system can overlap
-    float* fw = reinterpret_cast<float*>(smem_raw);            // [16][max_splits] weights 2^(m_sp - M) / L
-    for (int idx = threadIdx.x; idx < n_heads * 32; idx += AD_THREADS) {
-        const int row = idx >> 5, ln = idx & 31;               // one warp per head
-        const size_t base = ((size_t)seq * n_q + head0 + row) * max_splits;
-        float m = -INFINITY;
-        for (int sp = ln; sp < n_splits; sp += 32) m = fmaxf(m, __ldcg(part_ml + (base + sp) * 2));
-        m = warp_max(m);
-        float l = 0.0f;
-        for (int sp = ln; sp < n_splits; sp += 32) {
-            const float ms = __ldcg(part_ml + (base + sp) * 2);
-            const float f = (ms == -INFINITY) ? 0.0f : fast_exp2(ms - m);
-            fw[row * max_splits + sp] = f;
-            l += __ldcg(part_ml + (base + sp) * 2 + 1) * f;
-        }
-        l = warp_sum(l);
-        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-        __syncwarp();
-        for (int sp = ln; sp < n_splits; sp += 32) fw[row * max_splits + sp] *= inv;
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < n_heads * D; idx += AD_THREADS) {
-        const int row = idx / D, e = idx - row * D;
-        const int head = head0 + row;
-        const float* po = part_o + ((size_t)seq * n_q + head) * max_splits * D + e;
-        const float* w = fw + row * max_splits;
-        float acc = 0.0f;
-#pragma unroll 8
-        for (int sp = 0; sp < n_splits; ++sp) acc = fmaf(__ldcg(po + (size_t)sp * D), w[sp], acc);
-        out[(size_t)seq * out_stride + (size_t)head * D + e] = __float2bfloat16_rn(acc);
-    }
 }
 
-// Merges the ranges of every (sequence, head) in range order: used for larger batches, where a
-// second launch costs less than a fence and a ticket in every block of the first.
+// Merges the ranges of every (sequence, head) in range order.
 template <int D>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
@@ -334,7 +284,7 @@ template <int D>
 static int launch_decode(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
                          const void* v_pages, const int* block_table, int table_stride, const int* seq_slot,
                          const int* seq_start, int n_seqs, int n_q, int n_kv, int window, float scale, int max_splits,
-                         float* part_o, float* part_ml, int* counters, cudaStream_t stream) {
+                         float* part_o, float* part_ml, cudaStream_t stream) {
     const int group = n_q / n_kv;
     const int head_chunks = (group + 15) / 16;
     const size_t smem = (size_t)4 * AD_TILE * D * sizeof(bf16);
@@ -350,9 +300,9 @@ static int launch_decode(const void* q, long q_stride, void* out, long out_strid
     const float scale_log2 = scale * 1.4426950408889634f;
     bfi_launch(kernel, grid, dim3(AD_THREADS), need, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,
                (const bf16*)k_pages, (const bf16*)v_pages, block_table, table_stride, seq_slot, seq_start, n_q, n_kv, window,
-               scale_log2, head_chunks, part_o, part_ml, counters);
+               scale_log2, head_chunks, part_o, part_ml);
     int rc = bfi_check_launch("attention_decode");
-    if (rc || max_splits == 1 || counters != nullptr) return rc;
+    if (rc || max_splits == 1) return rc;
     bfi_launch(attention_decode_merge_kernel<D>, dim3(n_q, n_seqs), dim3(D <= 64 ? 64 : 128), 0, stream,
                (const float*)part_o, (const float*)part_ml, seq_slot, seq_start, (bf16*)out, out_stride, n_q, max_splits,
                window);
@@ -361,14 +311,12 @@ static int launch_decode(const void* q, long q_stride, void* out, long out_strid
 
 // Returns 0 on success, 1 on error, 2 when the shape is not taken (nothing launched).
 // Every sequence's pages are cut into at most `max_splits` ranges.  With max_splits > 1 the caller
-// gives part_o [n_seqs*n_q*max_splits*d], part_ml [n_seqs*n_q*max_splits*2] floats and either
-// counters [n_seqs * n_kv * ceil(group/16)] ints that are zero (the call leaves them zero; the last
-// block of a sequence and kv head merges its ranges) or null (a second kernel merges).
+// gives part_o [n_seqs*n_q*max_splits*d] and part_ml [n_seqs*n_q*max_splits*2] floats.
 extern "C" int bfi_attention_decode_bf16(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
                                          const void* v_pages, const int* block_table, int table_stride,
                                          const int* seq_slot, const int* seq_start, int n_seqs, int n_q, int n_kv,
                                          int d, int window, float scale, int max_splits, float* part_o, float* part_ml,
-                                         int* counters, cudaStream_t stream) {
+                                         cudaStream_t stream) {
     BFI_REQUIRE(n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_decode: %d query heads do not divide into %d kv heads",
                 n_q, n_kv);
     BFI_REQUIRE(window >= 0 && max_splits >= 1 && max_splits <= 65535, "attention_decode: bad window or split count");
@@ -378,7 +326,7 @@ extern "C" int bfi_attention_decode_bf16(const void* q, long q_stride, void* out
     if (max_splits > 1) BFI_REQUIRE(part_o && part_ml, "attention_decode: split runs need the scratch buffers");
     if (d == 64)
         return launch_decode<64>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride, seq_slot,
-                                 seq_start, n_seqs, n_q, n_kv, window, scale, max_splits, part_o, part_ml, counters, stream);
+                                 seq_start, n_seqs, n_q, n_kv, window, scale, max_splits, part_o, part_ml, stream);
     return launch_decode<128>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride, seq_slot,
-                              seq_start, n_seqs, n_q, n_kv, window, scale, max_splits, part_o, part_ml, counters, stream);
+                              seq_start, n_seqs, n_q, n_kv, window, scale, max_splits, part_o, part_ml, stream);
 }

@@ -124,15 +124,12 @@ def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
     return False
 
 
-FUSED_MERGE_MAX_GROUPS = 16
-
-
 def decode_splits(n_seqs: int, n_kv: int, group: int, max_pages: int) -> int:
     """Into how many page ranges every (sequence, kv head) is cut: enough blocks to fill the GPU
-    once, never more than a sequence can have pages.  Depends only on sizes that are
-    fixed when a step is captured."""
+    once (two to three blocks are resident on an SM), never more than a sequence can have pages.
+    Depends only on sizes that are fixed when a step is captured."""
     blocks = n_seqs * n_kv * ((group + 15) // 16)
-    want = (SM_COUNT * 3 + blocks - 1) // blocks          # three blocks are resident on an SM: one wave
+    want = (SM_COUNT * 5 // 2 + blocks - 1) // blocks
     return max(1, min(want, max_pages, 32))
 
 
@@ -143,19 +140,15 @@ def attention_decode_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads
     max_pages = kv.block_table.shape[1]
     group = n_heads // kv.n_kv_heads
     max_splits = decode_splits(ctx.n_seqs, kv.n_kv_heads, group, max_pages)
-    part_o = part_ml = counters = None
+    part_o = part_ml = None
     if max_splits > 1:
         part_o = ctx.workspace.vector("attn.part_o", ctx.n_seqs * n_heads * max_splits * d, torch.float32)
         part_ml = ctx.workspace.vector("attn.part_ml", ctx.n_seqs * n_heads * max_splits * 2, torch.float32)
-        groups = ctx.n_seqs * kv.n_kv_heads * ((group + 15) // 16)
-        if groups <= FUSED_MERGE_MAX_GROUPS:
-            # few blocks: merging inside the kernel saves a launch; many: a second kernel is cheaper
-            _, counters = _split_scratch.get(qkv.device, 1, groups)
     return library("fast").call_optional(
         "bfi_attention_decode_bf16", _ptr(qkv), c_long(qkv.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(kv.k),
         _ptr(kv.v), _ptr(kv.block_table), c_int(kv.block_table.stride(0)), _ptr(ctx.seq_slot), _ptr(ctx.seq_start),
         c_int(ctx.n_seqs), c_int(n_heads), c_int(kv.n_kv_heads), c_int(d), c_int(kv.window or 0), c_float(scale),
-        c_int(max_splits), _ptr(part_o), _ptr(part_ml), _ptr(counters), _stream())
+        c_int(max_splits), _ptr(part_o), _ptr(part_ml), _stream())
 
 
 def attention_prefill_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float) -> bool:

@@ -68,11 +68,17 @@ attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
 
     // The sequence's older pages, its slot, position and page table were all written before this
     // step's kernels began; only the page of the new token (the last one) and q come from the
-    // kernel before this one.  So the first tile, unless it is that page, travels before the wait.
-    const bool early_tile = p_beg < p_end && p_beg != last_page;
-    if (early_tile) issue(p_beg, 0);
+    // kernel before this one.  So the first two tiles, unless they are that page, travel before the wait.
+    int issued = 0;                                       // tiles on their way
+    while (issued < 2 && p_beg + issued < p_end && p_beg + issued != last_page) {
+        issue(p_beg + issued, issued);
+        ++issued;
+    }
     pdl_wait();
-    if (p_beg < p_end && !early_tile) issue(p_beg, 0);
+    if (issued == 0 && p_beg < p_end) {
+        issue(p_beg, 0);
+        issued = 1;
+    }
 
     // query fragments: rows g and g+8 are heads head0+g, head0+g+8
     const bf16* qbase = q + (size_t)seq * q_stride;       // one token per sequence: row index = seq
@@ -102,7 +108,10 @@ attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
     for (int p = p_beg; p < p_end; ++p) {
         const int stage = (p - p_beg) & 1;
         if (p + 1 < p_end) {
-            issue(p + 1, stage ^ 1);
+            if (p + 1 - p_beg >= issued) {
+                issue(p + 1, stage ^ 1);
+                ++issued;
+            }
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();

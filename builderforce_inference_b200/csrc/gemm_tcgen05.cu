@@ -437,8 +437,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         pdl_wait();                                      // C may still be in use by the kernel before
         const int quad = warp & 3;
         int local = 0;
-        bool alive = true;
-        for (int tile = blockIdx.x; alive && tile < n_tiles; tile += gridDim.x, ++local) {
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
             int tm, tn;
             tile_coords(tile, tm, tn);
             const int full_idx = HALVES == 1 ? (local & 1) : 0;
@@ -753,8 +752,6 @@ static int launch_tc_prefill(const void* A, long lda, const void* W, long ldw, v
     rc = bfi_tensor_map_bf16(W, N, K, ldw, tile_n, &mw);
     if (rc) return rc;
     // whole 16-byte stores need aligned rows: output row stride and base
-    const int out_cols_shift = epilogue == EPI_SWIGLU ? 1 : 0;
-    (void)out_cols_shift;
     const int elem = dtype_size(c_dtype);
     const int vec_ok = ((ldc * elem) % 16 == 0 && ((uintptr_t)C & 15) == 0) ? 1 : 0;
     if (halves == 2)

@@ -108,12 +108,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     constexpr int S_COLS = FT_KEYS;                        // columns of one S buffer
     constexpr int O_COL = 2 * S_COLS;                      // O behind the two S buffers
 
-    const int seq = blockIdx.z;
+    // Blocks are handed to the SMs in the order x, y, z: the token tile is z, counted from the end,
+    // so that every head's and sequence's longest tiles run first and the short ones fill the tail.
+    const int seq = blockIdx.y;
     const int slot = seq_slot[seq];
     if (slot < 0) return;
     const int t0 = cu_seqlens[seq];
     const int nt = cu_seqlens[seq + 1] - t0;
-    const int tok0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * FT_ROWS;       // long tiles are launched first
+    const int tok0 = ((int)gridDim.z - 1 - (int)blockIdx.z) * FT_ROWS;
     if (tok0 >= nt) return;
 
     extern __shared__ unsigned char smem_raw[];
@@ -136,7 +138,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int start = seq_start[seq];
-    const int head = blockIdx.y;
+    const int head = blockIdx.x;
     const int kvh = head / (n_q / n_kv);
     const int seq_hi = start + nt - 1;                                  // last position the cache holds
     const int p0 = start + tok0;                                        // position of the block's first token
@@ -442,7 +444,7 @@ static int launch_prefill_tc(const void* qkv, long q_stride, void* out, long out
                                           cudaGetErrorString(e));
     const unsigned lbo = FT_BOX_BYTES;      // leading byte offset: between the two 64-wide halves of the head
     const unsigned sbo = 1024;              // stride byte offset: between groups of 8 keys
-    dim3 grid((max_seq_tokens + FT_ROWS - 1) / FT_ROWS, n_q, n_seqs);
+    dim3 grid(n_q, n_seqs, (max_seq_tokens + FT_ROWS - 1) / FT_ROWS);
     bfi_launch(kernel, grid, dim3(FT_THREADS), smem, stream, mq, mk, mv, (bf16*)out, out_stride, block_table, table_stride,
                cu_seqlens, seq_slot, seq_start, n_q, n_kv, window, scale * 1.4426950408889634f, (uint32_t)lbo, (uint32_t)sbo,
                status);
@@ -466,7 +468,8 @@ extern "C" int bfi_attention_prefill_tcgen05_bf16(const void* qkv, long q_stride
     if (n_seqs <= 0 || max_seq_tokens <= 0) return 0;
     if (d != 64 && d != 128) return 2;
     if (q_stride % 8 != 0 || out_stride % 8 != 0 || ((uintptr_t)qkv & 15) || ((uintptr_t)out & 15) ||
-        ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) || n_seqs > 65535 || n_q > 65535)
+        ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) || n_seqs > 65535 ||
+        (max_seq_tokens + FT_ROWS - 1) / FT_ROWS > 65535)
         return 2;
     if (n_pages * n_kv * FT_PAGE > 0x7fffffffL) return 2;       // TMA coordinates are 32-bit
     if (d == 64)

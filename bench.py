@@ -205,7 +205,8 @@ KERNEL_SHAPES = {"qkv": (6144, 2560, 0), "o": (2560, 4096, 1), "gateup": (19456,
 def kernel_run(a) -> int:
     """Times ONE kernel on one workload (for profiling under ncu and for the files in profiles/):
     ``--kernel skinny_gemm|gemm_tcgen05 --shape qkv|o|gateup|down|head --rows M`` or
-    ``--kernel attention_decode|attention_prefill|attention_prefill_tcgen05 --rows B_or_T --ctx C``,
+    ``--kernel attention_decode|attention_prefill|attention_prefill_tcgen05 --rows B_or_T --ctx C``
+    (``--seqs N``: N prompts of --rows tokens each),
     ``--kernel qk_norm_rope --rows T``.  Weights rotate over
     enough copies to exceed L2.  Prints one JSON line."""
     import torch
@@ -258,7 +259,7 @@ def kernel_run(a) -> int:
         c = CONFIG_4B
         nq, nkv, d = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"]
         decode = a.kernel == "attention_decode"
-        n_seq = a.rows if decode else 1
+        n_seq = a.rows if decode else a.seqs
         t_new = 1 if decode else a.rows
         ctx_len = a.ctx if decode else t_new
         blocks = (ctx_len + 63) // 64
@@ -288,7 +289,7 @@ def kernel_run(a) -> int:
             if not fn(ctx, q, out, kvs[i % copies], nq, d ** -0.5):
                 raise SystemExit(f"{a.kernel} does not take this shape")
         bytes_moved = n_seq * ctx_len * 2 * nkv * d * 2
-        flops = 4.0 * nq * d * (n_seq * ctx_len if decode else t_new * (t_new + 1) / 2)
+        flops = 4.0 * nq * d * n_seq * (ctx_len if decode else t_new * (t_new + 1) / 2)
         what = {"seqs": n_seq, "new_tokens": t_new, "context": ctx_len, "q_heads": nq, "kv_heads": nkv, "head_dim": d}
     for i in range(3):
         one(i)
@@ -323,6 +324,7 @@ def kernel_run(a) -> int:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--seqs", type=int, default=1, help="kernel mode, prompt attention: prompts of --rows tokens each")
     ap.add_argument("--kernel", default=None, choices=["skinny_gemm", "gemm_tcgen05", "qk_norm_rope", "attention_decode",
                                                        "attention_prefill", "attention_prefill_tcgen05"],
                     help="time one kernel instead of the model (see kernel_run)")

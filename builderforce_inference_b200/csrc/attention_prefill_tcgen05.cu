@@ -2,9 +2,13 @@
 // attends causally over the cached keys and values of its sequence (the step's own tokens are
 // already in the cache), with an optional window (crates/bfi-core/src/cpu.rs:328-392).
 //
-// One block per (sequence, query head, 128 consecutive tokens).  Keys and values arrive as tiles
-// of 128 positions (two cache pages) by TMA with the 128-byte swizzle; both products run as
-// tcgen05.mma with float32 accumulators in tensor memory:
+// A work item is (sequence, query head, 128 consecutive tokens).  One block per SM draws items
+// from a shared ticket counter until none is left: the token tiles from the last one down (the
+// longest first, the short ones fill the tail), and within a tile index sequences and heads.  The
+// rings of keys and values, the two score buffers and the tensor cores run on from one item into
+// the next, so that an item's start-up and its output hide behind its neighbours' products.  Keys
+// and values arrive as tiles of 128 positions (two cache pages) by TMA with the 128-byte swizzle;
+// both products run as tcgen05.mma with float32 accumulators in tensor memory:
 //
 //   S = Q K^T    Q [128 tokens x D] and K [128 keys x D] from shared memory, S in tensor memory
 //                (one lane per token, one column per key), double-buffered
@@ -16,8 +20,10 @@
 //              P = 2^(s*c - m*c) back as bfloat16 (tcgen05.st).  The running maximum m is only
 //              raised when a row maximum exceeds it by more than 8 in the exponent; then the
 //              thread rescales its row of O in tensor memory.  The sum of P is kept in float32.
-//              At the end the thread divides its row of O by the sum and stores it.
-//   warp 4     TMA producer: Q once, then K and V tiles through rings of two stages.  Rows of a V
+//              One tile into the next item (O is double-buffered too) the thread divides its row
+//              of the finished item's O by the sum and stores it.
+//   warp 4     TMA producer: draws the items, writes each item's record for the other warps,
+//              loads its Q tile (two buffers), then K and V tiles through rings of two stages.  Rows of a V
 //              tile that the cache never wrote (after the sequence's last position, or in a page
 //              the sequence does not hold) are cleared in shared memory, so that a weight of
 //              zero cannot meet a stray NaN.
@@ -35,6 +41,7 @@
 #define FT_PAGE 64
 #define FT_BOX_BYTES (128 * 128)      // a box of 128 rows x 64 bfloat16
 #define FT_RESCALE_ABOVE 8.0f         // in the exponent of 2: P stays below 2^8
+#define FT_META_SEQS 512              // sequences whose numbers a block keeps in shared memory
 
 // 32 consecutive columns of this thread's lane; the caller waits with tmem_wait_ld()
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
@@ -95,69 +102,129 @@ __device__ __forceinline__ uint32_t ft_pack(float lo, float hi) {
 }
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+// A warp of the softmax group writes its 32 rows of a finished item's O, divided by the rows'
+// sums, to `dst` (the warp's first row).  Rows leave through the warp's staging tile in shared
+// memory (32 rows x 128 bytes, 16-byte units XOR-swizzled by the row), so that a store instruction
+// of the warp writes four whole 128-byte lines instead of 16 bytes of 32 different rows.
+template <int D>
+__device__ __noinline__ bool ft_write_out(uint64_t* o_done, uint32_t parity, uint64_t* o_free, uint32_t o_addr, float l_sum,
+                                          bf16* dst, long out_stride, int rows_here, uint32_t stage) {
+    const int lane = threadIdx.x & 31;
+    if (!__all_sync(0xffffffffu, mbar_wait(o_done, parity))) return false;
+    tc_fence_after();
+    const float inv = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
+    float o[D];
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) tmem_ld32(o_addr + c * 32, o + c * 32);
+    tmem_wait_ld();
+    tc_fence_before();
+    mbar_arrive(o_free);                                   // the rows are in registers: the tensor cores may have the buffer
+#pragma unroll
+    for (int c = 0; c < D / 64; ++c) {
+#pragma unroll
+        for (int e = 0; e < 64; e += 8) {
+            const float* v = o + c * 64 + e;
+            uint4 w;
+            w.x = ft_pack(v[0] * inv, v[1] * inv);
+            w.y = ft_pack(v[2] * inv, v[3] * inv);
+            w.z = ft_pack(v[4] * inv, v[5] * inv);
+            w.w = ft_pack(v[6] * inv, v[7] * inv);
+            sts128(stage + lane * 128 + (((e >> 3) ^ (lane & 7)) << 4), w);
+        }
+        __syncwarp();
+        uint4 w[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int row = k * 4 + (lane >> 3);
+            w[k] = lds128(stage + row * 128 + (((lane & 7) ^ (row & 7)) << 4));
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int row = k * 4 + (lane >> 3);
+            if (row < rows_here) *reinterpret_cast<uint4*>(dst + (size_t)row * out_stride + c * 64 + (lane & 7) * 8) = w[k];
+        }
+        __syncwarp();
+    }
+    return true;
+}
+
+// What the producer tells the other warps about a work item (one per Q buffer).
+struct FtItem {
+    int n_tiles;      // key tiles of the item; 0: there is no further item
+    int j_beg;        // first key tile
+    int p0;           // position of the item's first token
+    int seq_hi;       // last position the cache holds for the sequence
+    int row0;         // row of the item's first token in q and out
+    int rows;         // tokens of the item that exist (at most FT_ROWS)
+    int head;
+    int pad;
+};
+
 template <int D>
 __global__ void __launch_bounds__(FT_THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, long out_stride,
                             const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_seqlens,
-                            const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int n_q, int n_kv,
-                            int window, float scale_log2, uint32_t v_lbo, uint32_t v_sbo, int* __restrict__ status) {
+                            const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int n_seqs, int max_tiles,
+                            int n_q, int n_kv, int window, float scale_log2, uint32_t v_lbo, uint32_t v_sbo,
+                            int* __restrict__ status, int* __restrict__ counters) {
     constexpr int BOXES = D / 64;
-    constexpr int TILE_BYTES = BOXES * FT_BOX_BYTES;       // the Q tile, a K tile or a V tile
+    constexpr int TILE_BYTES = BOXES * FT_BOX_BYTES;       // a Q tile, a K tile or a V tile
     constexpr int PAGE_BYTES = FT_PAGE * 128;              // one page's rows inside a box
     constexpr int S_COLS = FT_KEYS;                        // columns of one S buffer
-    constexpr int O_COL = 2 * S_COLS;                      // O behind the two S buffers
-
-    // Blocks are handed to the SMs in the order x, y, z: the token tile is z, counted from the end,
-    // so that every head's and sequence's longest tiles run first and the short ones fill the tail.
-    const int seq = blockIdx.y;
-    const int slot = seq_slot[seq];
-    if (slot < 0) return;
-    const int t0 = cu_seqlens[seq];
-    const int nt = cu_seqlens[seq + 1] - t0;
-    const int tok0 = ((int)gridDim.z - 1 - (int)blockIdx.z) * FT_ROWS;
-    if (tok0 >= nt) return;
+    constexpr int O_COL = 2 * S_COLS;                      // the two O buffers behind the two S buffers
+    constexpr uint32_t FULL = 0xffffffffu;
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char* q_smem = smem;
-    unsigned char* k_smem = q_smem + TILE_BYTES;            // [2] stages
+    unsigned char* q_smem = smem;                           // [2] items
+    unsigned char* k_smem = q_smem + 2 * TILE_BYTES;        // [2] stages
     unsigned char* v_smem = k_smem + 2 * TILE_BYTES;        // [2] stages
     uint64_t* bars = reinterpret_cast<uint64_t*>(v_smem + 2 * TILE_BYTES);
-    uint64_t* q_full = bars;
-    uint64_t* k_full = bars + 1;      // [2]
-    uint64_t* k_empty = bars + 3;     // [2]
-    uint64_t* v_full = bars + 5;      // [2]
-    uint64_t* v_empty = bars + 7;     // [2]
-    uint64_t* s_full = bars + 9;      // [2]
-    uint64_t* p_full = bars + 11;     // [2]
-    uint64_t* o_ready = bars + 13;
-    uint64_t* tail_bar = bars + 14;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+    uint64_t* q_full = bars;          // [2] the item's record is written and its Q tile has landed
+    uint64_t* q_empty = bars + 2;     // [2] the item's products with Q are done and every warp has read its record
+    uint64_t* k_full = bars + 4;      // [2]
+    uint64_t* k_empty = bars + 6;     // [2]
+    uint64_t* v_full = bars + 8;      // [2]
+    uint64_t* v_empty = bars + 10;    // [2]
+    uint64_t* s_full = bars + 12;     // [2]
+    uint64_t* p_full = bars + 14;     // [2]
+    uint64_t* o_tile = bars + 16;     // every P V product, one phase per tile
+    uint64_t* o_done = bars + 17;     // [2] an item's last P V product
+    uint64_t* o_free = bars + 19;     // [2] the softmax warps have read the item's O
+    uint64_t* tail_bar = bars + 21;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 22);
     volatile int* s_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile FtItem* items = reinterpret_cast<volatile FtItem*>(tmem_slot + 2);     // [2]
+    int4* seq_meta = reinterpret_cast<int4*>(smem + 6 * TILE_BYTES + 512);          // [FT_META_SEQS]
+    unsigned char* stage_smem = reinterpret_cast<unsigned char*>(seq_meta + FT_META_SEQS);   // [4 warps][32 rows][128 bytes]
+    const bool meta_in_smem = n_seqs <= FT_META_SEQS;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int start = seq_start[seq];
-    const int head = blockIdx.x;
-    const int kvh = head / (n_q / n_kv);
-    const int seq_hi = start + nt - 1;                                  // last position the cache holds
-    const int p0 = start + tok0;                                        // position of the block's first token
-    const int hi_block = start + min(tok0 + FT_ROWS - 1, nt - 1);
-    const int lo_block = window > 0 ? max(0, p0 - window + 1) : 0;
-    const int j_beg = lo_block / FT_KEYS, j_end = hi_block / FT_KEYS;   // key tiles, inclusive
-    const int n_tiles = j_end - j_beg + 1;
 
     if (threadIdx.x == 0) {
-        mbar_init(q_full, 1);
         for (int s = 0; s < 2; ++s) {
+            mbar_init(&q_full[s], 1);
+            mbar_init(&q_empty[s], 1 + FT_ROWS / 32);
             mbar_init(&k_full[s], 1);
             mbar_init(&k_empty[s], 1);
             mbar_init(&v_full[s], 1);
             mbar_init(&v_empty[s], 1);
             mbar_init(&s_full[s], 1);
             mbar_init(&p_full[s], FT_ROWS);
+            mbar_init(&o_done[s], 1);
+            mbar_init(&o_free[s], FT_ROWS);
         }
-        mbar_init(o_ready, 1);
+        mbar_init(o_tile, 1);
         mbar_init(tail_bar, 1);
         *s_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -166,6 +233,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
+    // every sequence's slot, first row, number of new tokens and first position (written before
+    // the step's first kernel began, so they may be read ahead of the wait)
+    if (meta_in_smem)
+        for (int q = threadIdx.x; q < n_seqs; q += FT_THREADS) {
+            const int t0 = cu_seqlens[q];
+            seq_meta[q] = make_int4(seq_slot[q], t0, cu_seqlens[q + 1] - t0, seq_start[q]);
+        }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -175,73 +249,153 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     if (warp == 4) {
         // ---------------------------------------------------------------- TMA producer
-        const int* table = block_table + (size_t)slot * table_stride;
-        if (lane == 0) {
-            mbar_expect_tx(q_full, TILE_BYTES);
-            for (int c = 0; c < BOXES; ++c) tma_load_2d(q_smem + c * FT_BOX_BYTES, &map_q, head * D + c * 64, t0 + tok0, q_full);
-        }
-        uint32_t tail_phase = 0;
-        bool failed = false;
-        for (int i = 0; i < n_tiles; ++i) {
-            const int j = j_beg + i, st = i & 1;
-            const uint32_t ph = (i >> 1) & 1;
-            int pg[2];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int idx = 2 * j + h;
-                pg[h] = idx < table_stride ? table[idx] : -1;
+        const int per_level = n_seqs * n_q;
+        const int total = max_tiles * per_level;
+        auto meta_of = [&](int seq) -> int4 {              // slot, first row, new tokens, first position
+            if (meta_in_smem) return seq_meta[seq];
+            const int t0 = cu_seqlens[seq];
+            return make_int4(seq_slot[seq], t0, cu_seqlens[seq + 1] - t0, seq_start[seq]);
+        };
+        // Items in the order: token tiles from the last one down (the longest first, so that the
+        // short ones fill the tail), sequences, heads.  Tickets come from a counter that all blocks
+        // share; an item is prepared (its sequence's numbers, the page ids of its first key tile)
+        // while the last tiles of the item before it are loaded.
+        struct Prep {
+            int have, head, kvh, tok0, slot, t0, nt, start, j_beg, n_tiles, pg0, pg1;
+        };
+        int drawn = 0;                                     // lane 0: the ticket drawn last
+        auto draw = [&]() {
+            if (lane == 0) drawn = atomicAdd(&counters[0], 1);
+        };
+        auto page_of = [&](int slot, int idx) -> int {
+            return idx < table_stride ? block_table[(size_t)slot * table_stride + idx] : -1;
+        };
+        auto prepare = [&]() -> Prep {                     // takes the ticket drawn before, draws on while items do not exist
+            Prep p = {};
+            for (;; draw()) {
+                const int v = __shfl_sync(FULL, drawn, 0);
+                if (v >= total) return p;
+                const int lvl = v / per_level, rem = v - lvl * per_level;
+                const int seq = rem / n_q;
+                const int4 m = meta_of(seq);
+                p.tok0 = (max_tiles - 1 - lvl) * FT_ROWS;
+                if (m.x < 0 || p.tok0 >= m.z) continue;
+                p.have = 1;
+                p.head = rem - seq * n_q;
+                p.kvh = p.head / (n_q / n_kv);
+                p.slot = m.x, p.t0 = m.y, p.nt = m.z, p.start = m.w;
+                const int p0 = p.start + p.tok0;                                      // position of the item's first token
+                const int hi_block = p.start + min(p.tok0 + FT_ROWS - 1, p.nt - 1);
+                const int lo_block = window > 0 ? max(0, p0 - window + 1) : 0;
+                p.j_beg = lo_block / FT_KEYS;
+                p.n_tiles = hi_block / FT_KEYS - p.j_beg + 1;                          // key tiles
+                p.pg0 = page_of(p.slot, 2 * p.j_beg);
+                p.pg1 = page_of(p.slot, 2 * p.j_beg + 1);
+                return p;
             }
-            const int n_have = (pg[0] >= 0) + (pg[1] >= 0);
-            unsigned char* kt = k_smem + (size_t)st * TILE_BYTES;
-            unsigned char* vt = v_smem + (size_t)st * TILE_BYTES;
+        };
+        // Hands an item to the other warps: waits for its Q buffer, writes its record and loads its
+        // Q tile -- or, when there is no further item, a record that says so.
+        auto announce = [&](int it, const Prep& p) -> bool {
+            const int qi = it & 1;
             int ok = 1;
             if (lane == 0) {
-                if (i >= 2 && !mbar_wait(&k_empty[st], ph ^ 1)) ok = 0;
-                if (ok) {
-                    mbar_expect_tx(&k_full[st], n_have * BOXES * PAGE_BYTES);
-                    for (int h = 0; h < 2; ++h)
-                        if (pg[h] >= 0)
-                            for (int c = 0; c < BOXES; ++c)
-                                tma_load_2d(kt + c * FT_BOX_BYTES + h * PAGE_BYTES, &map_k, c * 64, (pg[h] * n_kv + kvh) * FT_PAGE,
-                                            &k_full[st]);
-                    if (i >= 2 && !mbar_wait(&v_empty[st], ph ^ 1)) ok = 0;
+                if (it >= 2 && !mbar_wait(&q_empty[qi], ((uint32_t)(it >> 1) & 1) ^ 1)) ok = 0;
+                if (ok && !p.have) {
+                    items[qi].n_tiles = 0;
+                    mbar_arrive(&q_full[qi]);
+                } else if (ok) {
+                    items[qi].n_tiles = p.n_tiles;
+                    items[qi].j_beg = p.j_beg;
+                    items[qi].p0 = p.start + p.tok0;
+                    items[qi].seq_hi = p.start + p.nt - 1;
+                    items[qi].row0 = p.t0 + p.tok0;
+                    items[qi].rows = p.nt - p.tok0;
+                    items[qi].head = p.head;
+                    mbar_expect_tx(&q_full[qi], TILE_BYTES);
+                    for (int c = 0; c < BOXES; ++c)
+                        tma_load_2d(q_smem + (size_t)qi * TILE_BYTES + c * FT_BOX_BYTES, &map_q, p.head * D + c * 64,
+                                    p.t0 + p.tok0, &q_full[qi]);
                 }
             }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) { failed = true; break; }
-            if (__shfl_sync(0xffffffffu, *s_flag, 0)) break;
-            const bool fix = n_have < 2 || j * FT_KEYS + FT_KEYS - 1 > seq_hi;
-            if (!fix) {
+            return __shfl_sync(FULL, ok, 0) != 0;
+        };
+        draw();
+        Prep cur = prepare(), nxt = {};
+        uint32_t g = 0, tail_phase = 0;                    // g counts key tiles over all items
+        bool failed = !announce(0, cur);
+        for (int it = 0; !failed && cur.have; ++it, cur = nxt) {
+            int ok = 1;
+            const int kvh = cur.kvh, slot = cur.slot, j_beg = cur.j_beg, n_tiles = cur.n_tiles;
+            const int seq_hi = cur.start + cur.nt - 1;                          // last position the cache holds
+            int pg_next[2] = {cur.pg0, cur.pg1};
+            for (int i = 0; i < n_tiles; ++i, ++g) {
+                const int j = j_beg + i, st = g & 1;
+                const uint32_t ph = (g >> 1) & 1;
+                const int pg[2] = {pg_next[0], pg_next[1]};
+                if (i + 1 < n_tiles) {                     // the next tile's page ids travel while this tile is handled
+                    pg_next[0] = page_of(slot, 2 * j + 2);
+                    pg_next[1] = page_of(slot, 2 * j + 3);
+                }
+                const int n_have = (pg[0] >= 0) + (pg[1] >= 0);
+                unsigned char* kt = k_smem + (size_t)st * TILE_BYTES;
+                unsigned char* vt = v_smem + (size_t)st * TILE_BYTES;
                 if (lane == 0) {
-                    mbar_expect_tx(&v_full[st], 2 * BOXES * PAGE_BYTES);
-                    for (int h = 0; h < 2; ++h)
-                        for (int c = 0; c < BOXES; ++c)
-                            tma_load_2d(vt + c * FT_BOX_BYTES + h * PAGE_BYTES, &map_v, c * 64, (pg[h] * n_kv + kvh) * FT_PAGE,
-                                        &v_full[st]);
+                    if (g >= 2 && !mbar_wait(&k_empty[st], ph ^ 1)) ok = 0;
+                    if (ok) {
+                        mbar_expect_tx(&k_full[st], n_have * BOXES * PAGE_BYTES);
+                        for (int h = 0; h < 2; ++h)
+                            if (pg[h] >= 0)
+                                for (int c = 0; c < BOXES; ++c)
+                                    tma_load_2d(kt + c * FT_BOX_BYTES + h * PAGE_BYTES, &map_k, c * 64,
+                                                (pg[h] * n_kv + kvh) * FT_PAGE, &k_full[st]);
+                        if (g >= 2 && !mbar_wait(&v_empty[st], ph ^ 1)) ok = 0;
+                    }
                 }
-            } else {
-                // the tile has rows the cache never wrote: land it first, clear those rows, then hand it over
-                if (lane == 0 && n_have > 0) {
-                    mbar_expect_tx(tail_bar, n_have * BOXES * PAGE_BYTES);
-                    for (int h = 0; h < 2; ++h)
-                        if (pg[h] >= 0)
-                            for (int c = 0; c < BOXES; ++c)
-                                tma_load_2d(vt + c * FT_BOX_BYTES + h * PAGE_BYTES, &map_v, c * 64,
-                                            (pg[h] * n_kv + kvh) * FT_PAGE, tail_bar);
-                    if (!mbar_wait(tail_bar, tail_phase)) ok = 0;
-                }
-                if (n_have > 0) tail_phase ^= 1;
-                ok = __shfl_sync(0xffffffffu, ok, 0);
+                ok = __shfl_sync(FULL, ok, 0);
                 if (!ok) { failed = true; break; }
-                for (int idx = lane; idx < FT_KEYS * 8 * BOXES; idx += 32) {
-                    const int row = idx / (8 * BOXES), rest = idx - row * (8 * BOXES);
-                    const int c = rest >> 3, chunk = rest & 7;
-                    const bool stale = pg[row / FT_PAGE] < 0 || j * FT_KEYS + row > seq_hi;
-                    if (stale) *reinterpret_cast<uint4*>(vt + c * FT_BOX_BYTES + row * 128 + chunk * 16) = make_uint4(0u, 0u, 0u, 0u);
+                if (__shfl_sync(FULL, *s_flag, 0)) { failed = true; break; }
+                const bool fix = n_have < 2 || j * FT_KEYS + FT_KEYS - 1 > seq_hi;
+                if (!fix) {
+                    if (lane == 0) {
+                        mbar_expect_tx(&v_full[st], 2 * BOXES * PAGE_BYTES);
+                        for (int h = 0; h < 2; ++h)
+                            for (int c = 0; c < BOXES; ++c)
+                                tma_load_2d(vt + c * FT_BOX_BYTES + h * PAGE_BYTES, &map_v, c * 64, (pg[h] * n_kv + kvh) * FT_PAGE,
+                                            &v_full[st]);
+                    }
+                } else {
+                    // the tile has rows the cache never wrote: land it first, clear those rows, then hand it over
+                    if (lane == 0 && n_have > 0) {
+                        mbar_expect_tx(tail_bar, n_have * BOXES * PAGE_BYTES);
+                        for (int h = 0; h < 2; ++h)
+                            if (pg[h] >= 0)
+                                for (int c = 0; c < BOXES; ++c)
+                                    tma_load_2d(vt + c * FT_BOX_BYTES + h * PAGE_BYTES, &map_v, c * 64,
+                                                (pg[h] * n_kv + kvh) * FT_PAGE, tail_bar);
+                        if (!mbar_wait(tail_bar, tail_phase)) ok = 0;
+                    }
+                    if (n_have > 0) tail_phase ^= 1;
+                    ok = __shfl_sync(FULL, ok, 0);
+                    if (!ok) { failed = true; break; }
+                    for (int idx = lane; idx < FT_KEYS * 8 * BOXES; idx += 32) {
+                        const int row = idx / (8 * BOXES), rest = idx - row * (8 * BOXES);
+                        const int c = rest >> 3, chunk = rest & 7;
+                        const bool stale = pg[row / FT_PAGE] < 0 || j * FT_KEYS + row > seq_hi;
+                        if (stale) *reinterpret_cast<uint4*>(vt + c * FT_BOX_BYTES + row * 128 + chunk * 16) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&v_full[st]);
                 }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&v_full[st]);
+                // The next item is drawn late, so that blocks that are ahead take more of what is
+                // left, but early enough to hide the ticket's and the Q tile's way: the ticket
+                // behind the third-last tile, the item itself behind the second-last one.
+                if (i == max(0, n_tiles - 3)) draw();
+                if (i == max(0, n_tiles - 2)) {
+                    nxt = prepare();
+                    if (!announce(it + 1, nxt)) { failed = true; break; }
+                }
             }
         }
         if (failed && lane == 0) {
@@ -253,42 +407,73 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (lane == 0) {
             constexpr uint32_t idesc_s = umma_idesc(FT_ROWS, FT_KEYS);
             constexpr uint32_t idesc_o = umma_idesc_b_mn(FT_ROWS, D);
-            const uint32_t q_addr = smem_u32(q_smem);
-            auto issue_qk = [&](int i) {          // S[i & 1] = Q K(i)^T
-                const uint32_t k_addr = smem_u32(k_smem + (size_t)(i & 1) * TILE_BYTES);
+            // Descriptors of the buffers' first bytes; a step inside a buffer adds its offset / 16 to
+            // the address field (the low 14 bits, which no buffer of this block overflows).
+            // (the second buffer of a pair lies TILE_BYTES behind the first)
+            const uint64_t q_desc = umma_desc_sw128(smem_u32(q_smem)), k_desc = umma_desc_sw128(smem_u32(k_smem));
+            const uint64_t v_desc = umma_desc_mn_sw128(smem_u32(v_smem), v_lbo, v_sbo);
+            constexpr uint64_t SECOND = TILE_BYTES >> 4;
+            auto issue_qk = [&](int qi, uint32_t gt) {          // S[gt & 1] = Q(item) K(tile gt)^T
+                const uint64_t qd = q_desc + (qi ? SECOND : 0), kd = k_desc + ((gt & 1) ? SECOND : 0);
+                const uint32_t s_addr = tmem_base + (gt & 1) * S_COLS;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = (uint32_t)(kk >> 2) * FT_BOX_BYTES + (uint32_t)(kk & 3) * 32;
-                    umma_bf16(tmem_base + (uint32_t)(i & 1) * S_COLS, umma_desc_sw128(q_addr + off), umma_desc_sw128(k_addr + off),
-                              idesc_s, kk > 0);
+                    umma_bf16(s_addr, qd + (off >> 4), kd + (off >> 4), idesc_s, kk > 0);
                 }
+                umma_commit(&s_full[gt & 1]);
+                umma_commit(&k_empty[gt & 1]);
             };
-            bool ok = mbar_wait(q_full, 0) && mbar_wait(&k_full[0], 0);
-            if (ok) {
-                tc_fence_after();
-                issue_qk(0);
-                umma_commit(&s_full[0]);
-                umma_commit(&k_empty[0]);
-            }
-            for (int i = 0; ok && i < n_tiles && !*s_flag; ++i) {
-                const int b = i & 1;
-                const uint32_t ph = (i >> 1) & 1;
-                if (i + 1 < n_tiles) {
-                    if (!mbar_wait(&k_full[b ^ 1], ((i + 1) >> 1) & 1)) { ok = false; break; }
+            uint32_t g = 0;
+            bool ok = mbar_wait(&q_full[0], 0);
+            int n_cur = ok ? items[0].n_tiles : 0;
+            if (ok && n_cur > 0) {
+                ok = mbar_wait(&k_full[0], 0);
+                if (ok) {
                     tc_fence_after();
-                    issue_qk(i + 1);
-                    umma_commit(&s_full[b ^ 1]);
-                    umma_commit(&k_empty[b ^ 1]);
+                    issue_qk(0, 0);
+                    if (n_cur == 1) umma_commit(&q_empty[0]);
                 }
-                if (!mbar_wait(&p_full[b], ph) || !mbar_wait(&v_full[b], ph)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t v_addr = smem_u32(v_smem + (size_t)b * TILE_BYTES);
+            }
+            for (int it = 0; ok && n_cur > 0 && !*s_flag; ++it) {
+                const int qi = it & 1;
+                const uint32_t o_addr = tmem_base + O_COL + (uint32_t)qi * D;
+                int n_next = 0;
+                for (int i = 0; i < n_cur; ++i, ++g) {
+                    const uint32_t b = g & 1, ph = (g >> 1) & 1;
+                    // the next tile's scores go ahead of this tile's P V: the softmax of the next
+                    // tile then runs while the tensor cores work on this one
+                    if (i + 1 < n_cur) {
+                        if (!mbar_wait(&k_full[b ^ 1], ((g + 1) >> 1) & 1)) { ok = false; break; }
+                        tc_fence_after();
+                        issue_qk(qi, g + 1);
+                        if (i + 2 == n_cur) umma_commit(&q_empty[qi]);
+                    } else {
+                        // the item's last tile: the first tile of the next item, if there is one
+                        if (!mbar_wait(&q_full[qi ^ 1], (uint32_t)((it + 1) >> 1) & 1)) { ok = false; break; }
+                        n_next = items[qi ^ 1].n_tiles;
+                        if (n_next > 0) {
+                            if (!mbar_wait(&k_full[b ^ 1], ((g + 1) >> 1) & 1)) { ok = false; break; }
+                            tc_fence_after();
+                            issue_qk(qi ^ 1, g + 1);
+                            if (n_next == 1) umma_commit(&q_empty[qi ^ 1]);
+                        }
+                    }
+                    if (!mbar_wait(&p_full[b], ph) || !mbar_wait(&v_full[b], ph)) { ok = false; break; }
+                    // the item before the last one had this O buffer: its rows must have been read
+                    if (i == 0 && it >= 2 && !mbar_wait(&o_free[qi], ((uint32_t)(it >> 1) & 1) ^ 1)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t vd = v_desc + (b ? SECOND : 0);
+                    const uint32_t p_addr = tmem_base + b * S_COLS;
 #pragma unroll
-                for (int kk = 0; kk < FT_KEYS / 16; ++kk)       // 16 keys per step: 8 columns of packed P, 2048 bytes of V
-                    umma_bf16_a_tmem(tmem_base + O_COL, tmem_base + (uint32_t)b * S_COLS + kk * 8,
-                                     umma_desc_mn_sw128(v_addr + kk * 2048, v_lbo, v_sbo), idesc_o, (i > 0 || kk > 0));
-                umma_commit(&v_empty[b]);
-                umma_commit(o_ready);
+                    for (int kk = 0; kk < FT_KEYS / 16; ++kk)       // 16 keys per step: 8 columns of packed P, 2048 bytes of V
+                        umma_bf16_a_tmem(o_addr, p_addr + kk * 8, vd + (uint64_t)(kk * 2048 >> 4), idesc_o, (i > 0 || kk > 0));
+                    umma_commit(&v_empty[b]);
+                    umma_commit(o_tile);
+                    if (i + 1 == n_cur) umma_commit(&o_done[qi]);
+                }
+                if (!ok) break;
+                n_cur = n_next;
             }
             if (!ok) {
                 atomicOr(status, BFI_STATUS_TIMEOUT);
@@ -299,104 +484,112 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // ---------------------------------------------------------------- softmax and output
         const int r = threadIdx.x;                                       // token of this thread, TMEM lane
         const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
-        const int pos_r = min(p0 + r, seq_hi);
-        const int lo_r = window > 0 ? max(0, pos_r - window + 1) : 0;
-        float m_used = -INFINITY, l_run = 0.0f;
         bool ok = true, timed_out = false;
+        // The rows of an item's O are read, divided by the sums and stored one tile into the next
+        // item, when the tensor cores already have that tile's scores and the next tile's products.
+        bool pending = false;
+        int e_it = 0, e_row0 = 0, e_rows = 0, e_head = 0;
+        float e_l = 0.0f;
+        auto write_out = [&]() -> bool {
+            return ft_write_out<D>(&o_done[e_it & 1], (uint32_t)(e_it >> 1) & 1, &o_free[e_it & 1],
+                                   lane_base + O_COL + (uint32_t)(e_it & 1) * D, e_l,
+                                   out + (size_t)(e_row0 + warp * 32) * out_stride + (size_t)e_head * D, out_stride,
+                                   e_rows - warp * 32, smem_u32(stage_smem) + warp * 4096);
+        };
+        uint32_t g = 0;
         // every wait's outcome is agreed on by the whole warp: the tensor-memory accesses are warp-wide
-        for (int i = 0; i < n_tiles; ++i) {
-            if (__any_sync(0xffffffffu, *s_flag != 0)) { ok = false; break; }
-            const int j = j_beg + i, b = i & 1;
-            const uint32_t ph = (i >> 1) & 1;
-            if (!__all_sync(0xffffffffu, mbar_wait(&s_full[b], ph))) { ok = false; timed_out = true; break; }
-            tc_fence_after();
-            float s[FT_KEYS];
-            const uint32_t s_addr = lane_base + (uint32_t)b * S_COLS;
-#pragma unroll
-            for (int c = 0; c < FT_KEYS / 32; ++c) tmem_ld32(s_addr + c * 32, s + c * 32);
-            tmem_wait_ld();
-            const int key0 = j * FT_KEYS;
-            const bool masked = key0 + FT_KEYS - 1 > p0 || key0 + FT_KEYS - 1 > seq_hi ||
-                                (window > 0 && key0 < p0 + FT_ROWS - 1 - window + 1);
-            if (masked) {
-                const int hi = pos_r - key0, lo = lo_r - key0;       // keep lo <= index <= hi
-#pragma unroll
-                for (int e = 0; e < FT_KEYS; ++e)
-                    if (e > hi || e < lo) s[e] = -INFINITY;
-            }
-            float mx = s[0];
-#pragma unroll
-            for (int e = 1; e < FT_KEYS; ++e) mx = fmaxf(mx, s[e]);
-            // raise the running maximum only when a score would otherwise exceed 2^8 after the shift
-            const bool raise = mx > -INFINITY && (m_used == -INFINITY || (mx - m_used) * scale_log2 > FT_RESCALE_ABOVE);
-            if (__any_sync(0xffffffffu, raise && i > 0)) {
-                const float m_new = raise ? mx : m_used;
-                const float f = (raise && m_used > -INFINITY) ? ft_exp2((m_used - m_new) * scale_log2) : 1.0f;
-                if (!__all_sync(0xffffffffu, mbar_wait(o_ready, (uint32_t)((i - 1) & 1)))) {     // O holds tiles 0 .. i-1
-                    ok = false;
-                    timed_out = true;
-                    break;
-                }
+        for (int it = 0; ok; ++it) {
+            const int qi = it & 1;
+            if (!__all_sync(FULL, mbar_wait(&q_full[qi], (uint32_t)(it >> 1) & 1))) { ok = false; timed_out = true; break; }
+            const int n_tiles = items[qi].n_tiles, j_beg = items[qi].j_beg, p0 = items[qi].p0, seq_hi = items[qi].seq_hi;
+            const int row0 = items[qi].row0, rows = items[qi].rows, head = items[qi].head;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&q_empty[qi]);
+            if (n_tiles == 0) break;
+            const uint32_t o_addr = lane_base + O_COL + (uint32_t)qi * D;
+            const int pos_r = min(p0 + r, seq_hi);
+            const int lo_r = window > 0 ? max(0, pos_r - window + 1) : 0;
+            float m_used = -INFINITY, l_run = 0.0f;
+            for (int i = 0; i < n_tiles; ++i, ++g) {
+                if (__any_sync(FULL, *s_flag != 0)) { ok = false; break; }
+                const int j = j_beg + i;
+                const uint32_t b = g & 1, ph = (g >> 1) & 1;
+                if (!__all_sync(FULL, mbar_wait(&s_full[b], ph))) { ok = false; timed_out = true; break; }
                 tc_fence_after();
+                float s[FT_KEYS];
+                const uint32_t s_addr = lane_base + b * S_COLS;
 #pragma unroll
-                for (int c = 0; c < D / 32; ++c) {
-                    float o[32];
-                    uint32_t ou[32];
-                    tmem_ld32(lane_base + O_COL + c * 32, o);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) ou[e] = __float_as_uint(o[e] * f);
-                    tmem_st32(lane_base + O_COL + c * 32, ou);
-                }
-                l_run *= f;
-                m_used = m_new;
-            } else if (raise) {
-                m_used = mx;                                          // first tile: nothing accumulated yet
-            }
-            const float mc = m_used == -INFINITY ? 0.0f : m_used * scale_log2;
-            float sum = 0.0f;
-            uint32_t pk[FT_KEYS / 2];
-#pragma unroll
-            for (int e = 0; e < FT_KEYS; e += 2) {
-                const float a = ft_exp2(fmaf(s[e], scale_log2, -mc));
-                const float c2 = ft_exp2(fmaf(s[e + 1], scale_log2, -mc));
-                sum += a + c2;
-                pk[e >> 1] = ft_pack(a, c2);
-            }
-            l_run += sum;
-#pragma unroll
-            for (int c = 0; c < FT_KEYS / 64; ++c) tmem_st32(s_addr + c * 32, pk + c * 32);
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(&p_full[b]);
-        }
-        if (ok && !__all_sync(0xffffffffu, mbar_wait(o_ready, (uint32_t)((n_tiles - 1) & 1)))) {
-            ok = false;
-            timed_out = true;
-        }
-        if (ok) {
-            tc_fence_after();
-            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            const bool store = tok0 + r < nt;
-            bf16* dst = out + (size_t)(t0 + tok0 + r) * out_stride + (size_t)head * D;
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-                float o[32];
-                tmem_ld32(lane_base + O_COL + c * 32, o);
+                for (int c = 0; c < FT_KEYS / 32; ++c) tmem_ld32(s_addr + c * 32, s + c * 32);
                 tmem_wait_ld();
-                if (store) {
+                const int key0 = j * FT_KEYS;
+                const bool masked = key0 + FT_KEYS - 1 > p0 || key0 + FT_KEYS - 1 > seq_hi ||
+                                    (window > 0 && key0 < p0 + FT_ROWS - 1 - window + 1);
+                if (masked) {
+                    // keep lo <= index <= hi; by groups of 32 keys, so that a warp passes over the
+                    // groups that all its rows keep whole (on the diagonal: those left of its rows)
+                    const int hi = pos_r - key0, lo = lo_r - key0;
 #pragma unroll
-                    for (int e = 0; e < 32; e += 8) {
-                        uint4 w;
-                        w.x = ft_pack(o[e] * inv, o[e + 1] * inv);
-                        w.y = ft_pack(o[e + 2] * inv, o[e + 3] * inv);
-                        w.z = ft_pack(o[e + 4] * inv, o[e + 5] * inv);
-                        w.w = ft_pack(o[e + 6] * inv, o[e + 7] * inv);
-                        *reinterpret_cast<uint4*>(dst + c * 32 + e) = w;
+                    for (int c = 0; c < FT_KEYS / 32; ++c) {
+                        if (__all_sync(FULL, c * 32 + 31 <= hi && c * 32 >= lo)) continue;
+#pragma unroll
+                        for (int e = c * 32; e < c * 32 + 32; ++e) s[e] = (e > hi || e < lo) ? -INFINITY : s[e];
                     }
                 }
+                float mx = s[0];
+#pragma unroll
+                for (int e = 1; e < FT_KEYS; ++e) mx = fmaxf(mx, s[e]);
+                // raise the running maximum only when a score would otherwise exceed 2^8 after the shift
+                const bool raise = mx > -INFINITY && (m_used == -INFINITY || (mx - m_used) * scale_log2 > FT_RESCALE_ABOVE);
+                if (__any_sync(FULL, raise && i > 0)) {
+                    const float m_new = raise ? mx : m_used;
+                    const float f = (raise && m_used > -INFINITY) ? ft_exp2((m_used - m_new) * scale_log2) : 1.0f;
+                    if (!__all_sync(FULL, mbar_wait(o_tile, (g - 1) & 1))) {     // O holds the item's tiles 0 .. i-1
+                        ok = false;
+                        timed_out = true;
+                        break;
+                    }
+                    tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        float o[32];
+                        uint32_t ou[32];
+                        tmem_ld32(o_addr + c * 32, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) ou[e] = __float_as_uint(o[e] * f);
+                        tmem_st32(o_addr + c * 32, ou);
+                    }
+                    l_run *= f;
+                    m_used = m_new;
+                } else if (raise) {
+                    m_used = mx;                                          // first tile: nothing accumulated yet
+                }
+                const float mc = m_used == -INFINITY ? 0.0f : m_used * scale_log2;
+                float sum = 0.0f;
+                uint32_t pk[FT_KEYS / 2];
+#pragma unroll
+                for (int e = 0; e < FT_KEYS; e += 2) {
+                    const float a = ft_exp2(fmaf(s[e], scale_log2, -mc));
+                    const float c2 = ft_exp2(fmaf(s[e + 1], scale_log2, -mc));
+                    sum += a + c2;
+                    pk[e >> 1] = ft_pack(a, c2);
+                }
+                l_run += sum;
+#pragma unroll
+                for (int c = 0; c < FT_KEYS / 64; ++c) tmem_st32(s_addr + c * 32, pk + c * 32);
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(&p_full[b]);
+                if (i == 0 && pending) {
+                    pending = false;
+                    if (!write_out()) { ok = false; timed_out = true; break; }
+                }
             }
+            if (!ok) break;
+            pending = true;
+            e_it = it, e_row0 = row0, e_rows = rows, e_head = head, e_l = l_run;
         }
+        if (ok && pending && !write_out()) timed_out = true;
         if (timed_out && lane == 0) {
             atomicOr(status, BFI_STATUS_TIMEOUT);
             *s_flag = 1;
@@ -407,8 +600,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __syncthreads();
     if (*s_flag && warp == 4 && lane == 0) {
         // a wait ran out: give outstanding TMA writes a bounded time to land
-        mbar_wait(q_full, 0);
         for (int s = 0; s < 2; ++s) {
+            mbar_wait(&q_full[s], 0), mbar_wait(&q_full[s], 1);
             mbar_wait(&k_full[s], 0), mbar_wait(&k_full[s], 1);
             mbar_wait(&v_full[s], 0), mbar_wait(&v_full[s], 1);
         }
@@ -418,6 +611,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (warp == 5) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
+    }
+    // the last block to finish puts the ticket counter back for the next launch
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(&counters[1], 1) == (int)gridDim.x - 1) {
+            counters[0] = 0;
+            counters[1] = 0;
+            __threadfence();
+        }
     }
 }
 
@@ -436,26 +638,38 @@ static int launch_prefill_tc(const void* qkv, long q_stride, void* out, long out
     if (rc) return rc;
     constexpr int TILE_BYTES = (D / 64) * FT_BOX_BYTES;
     // at least half an SM's shared memory, so that two blocks never share one SM's tensor memory
-    const size_t tiles = (size_t)5 * TILE_BYTES + 1024 + 256;
+    const size_t tiles = (size_t)6 * TILE_BYTES + 1024 + 512 + FT_META_SEQS * sizeof(int4) + 4 * 4096;
     const size_t smem = tiles > 120 * 1024 ? tiles : 120 * 1024;
     auto kernel = attention_prefill_tc_kernel<D>;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return bfi_fail("attention_prefill_tcgen05: cannot reserve %zu bytes of shared memory: %s", smem,
-                                          cudaGetErrorString(e));
+    static bool configured = false;
+    static int n_sm = 148;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return bfi_fail("attention_prefill_tcgen05: cannot reserve %zu bytes of shared memory: %s", smem,
+                                              cudaGetErrorString(e));
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+        configured = true;
+    }
     const unsigned lbo = FT_BOX_BYTES;      // leading byte offset: between the two 64-wide halves of the head
     const unsigned sbo = 1024;              // stride byte offset: between groups of 8 keys
-    dim3 grid(n_q, n_seqs, (max_seq_tokens + FT_ROWS - 1) / FT_ROWS);
+    const int max_tiles = (max_seq_tokens + FT_ROWS - 1) / FT_ROWS;
+    const long items = (long)max_tiles * n_seqs * n_q;
+    dim3 grid((unsigned)(items < n_sm ? items : n_sm));      // one block per SM, each drawing items until none is left
     bfi_launch(kernel, grid, dim3(FT_THREADS), smem, stream, mq, mk, mv, (bf16*)out, out_stride, block_table, table_stride,
-               cu_seqlens, seq_slot, seq_start, n_q, n_kv, window, scale * 1.4426950408889634f, (uint32_t)lbo, (uint32_t)sbo,
-               status);
+               cu_seqlens, seq_slot, seq_start, n_seqs, max_tiles, n_q, n_kv, window, scale * 1.4426950408889634f,
+               (uint32_t)lbo, (uint32_t)sbo, status, status + 1);
     return bfi_check_launch("attention_prefill_tcgen05");
 }
 
 // qkv [n_tokens, >= n_q*d] with the step's query heads (already normalised and rotated), the
 // cache pages [n_pages, n_kv, 64, d] holding every key and value up to each sequence's last new
 // token.  Returns 0 on success, 1 on error, 2 when the shape is not taken (nothing launched):
-// head sizes other than 64/128, or operands TMA cannot address.  A wait that ran out sets
-// BFI_STATUS_TIMEOUT in `status`.
+// head sizes other than 64/128, or operands TMA cannot address.  `status` points at three ints,
+// zero before the first call: [0] gets BFI_STATUS_TIMEOUT when a wait ran out, [1] and [2] are
+// the counters of tickets drawn and blocks finished, which every launch leaves at zero again; two
+// launches that may run at the same time need status words of their own.
 extern "C" int bfi_attention_prefill_tcgen05_bf16(const void* qkv, long q_stride, void* out, long out_stride,
                                                   const void* k_pages, const void* v_pages, long n_pages,
                                                   const int* block_table, int table_stride, const int* cu_seqlens,
@@ -468,8 +682,7 @@ extern "C" int bfi_attention_prefill_tcgen05_bf16(const void* qkv, long q_stride
     if (n_seqs <= 0 || max_seq_tokens <= 0) return 0;
     if (d != 64 && d != 128) return 2;
     if (q_stride % 8 != 0 || out_stride % 8 != 0 || ((uintptr_t)qkv & 15) || ((uintptr_t)out & 15) ||
-        ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) || n_seqs > 65535 ||
-        (max_seq_tokens + FT_ROWS - 1) / FT_ROWS > 65535)
+        ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) || (long)((max_seq_tokens + FT_ROWS - 1) / FT_ROWS) * n_seqs * n_q > 0x3fffffffL)
         return 2;
     if (n_pages * n_kv * FT_PAGE > 0x7fffffffL) return 2;       // TMA coordinates are 32-bit
     if (d == 64)

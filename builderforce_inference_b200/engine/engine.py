@@ -208,7 +208,7 @@ class Engine:
         if self.dtype == torch.bfloat16:
             from ..kernels import fast_ops
             tc = fast_ops.tc_status(self.device)
-            tc_bits = int(tc.item())
+            tc_bits = int(tc[0].item())
             if tc_bits:
                 tc.zero_()
                 raise StepError("device-side check failed: a bounded wait in the tensor-core matrix product ran out "

@@ -49,10 +49,11 @@ _tc_status = {}
 
 
 def tc_status(device) -> torch.Tensor:
-    """The word in which the tensor-core product records a bounded wait that ran out (bit 8)."""
+    """The word in which the tcgen05 kernels record a bounded wait that ran out (bit 8), followed
+    by the prompt attention's two counters (tickets drawn, blocks finished; zero between launches)."""
     t = _tc_status.get(device)
     if t is None:
-        t = torch.zeros(1, dtype=torch.int32, device=device)
+        t = torch.zeros(4, dtype=torch.int32, device=device)
         _tc_status[device] = t
     return t
 
@@ -167,8 +168,9 @@ TCGEN05_ATTENTION_MIN_TOKENS = 128     # shorter steps: the mma.sync kernel with
 
 
 def attention_prefill_tcgen05_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float) -> bool:
-    """tcgen05 / TMA attention for steps with long runs of new tokens: 128 tokens of one head per
-    block, scores and output in tensor memory.  A wait that ran out shows in ``tc_status``."""
+    """tcgen05 / TMA attention for steps with long runs of new tokens: one block per SM draws
+    items of 128 tokens of one head, scores and output in tensor memory.  A wait that ran out
+    shows in ``tc_status``."""
     d = kv.head_dim
     if d not in (64, 128) or qkv.dtype != torch.bfloat16 or kv.k.dtype != torch.bfloat16:
         return False

@@ -179,7 +179,7 @@ def tc_check(m, n, k, epi, seed=0):
         out = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
     assert fast().gemm_tcgen05(a.to(DEV), w.to(DEV), out, epi)
     torch.cuda.synchronize()
-    assert int(fast().tc_status(torch.device(DEV)).item()) == 0, "a bounded wait ran out"
+    assert int(fast().tc_status(torch.device(DEV))[0].item()) == 0, "a bounded wait ran out"
     assert rel_err(out.float(), ref) < (1e-2 if epi == 2 else 3e-5), (m, n, k, epi)
 
 
@@ -239,9 +239,10 @@ def prefill_kernel(name):
 
 def tc_status_clear():
     st = fast().tc_status(torch.device(DEV))
-    bits = int(st.item())
+    words = st.tolist()
     st.zero_()
-    return bits
+    assert words[1] == 0 and words[2] == 0, "the prompt attention left its ticket counters standing"
+    return words[0]
 
 
 @pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
@@ -337,6 +338,74 @@ def test_attention_prefill_tcgen05_long_and_ragged(d, window):
     for slot, start, t in seqs:
         assert rel_err(got[o:o + t], ref[o:o + t]) < 1e-2, (slot, start, t)
         o += t
+
+
+@pytest.mark.parametrize("window", [None, 150])
+def test_attention_prefill_tcgen05_many_items_per_block(window):
+    """Far more (sequence, head, 128-token tile) items than SMs, of unequal sizes, so that every
+    block runs through many items: its rings, score and output buffers and the shared ticket
+    counter carry on from one item into the next; some sequences are padding."""
+    n_q, n_kv, d = 8, 4, 128
+    g = gen(77)
+    lens = torch.randint(1, 640, (44,), generator=g).tolist()
+    starts = torch.randint(0, 130, (44,), generator=g).tolist()
+    seqs, slot = [], 0
+    for i, (start, t) in enumerate(zip(starts, lens)):
+        if i % 9 == 4:
+            seqs.append((-1, 0, t))
+        else:
+            seqs.append((slot, start if i % 3 else 0, t))
+            slot += 1
+    pages = Pages(slot, 800, n_kv, d, torch.bfloat16, window=window, seed=5)
+    scale = 1.0 / math.sqrt(d)
+    qs, refs = [], []
+    for sl, start, t in seqs:
+        n = start + t
+        k = torch.randn(n, n_kv, d, generator=g).bfloat16().float()
+        v = torch.randn(n, n_kv, d, generator=g).bfloat16().float()
+        qq = torch.randn(t, n_q, d, generator=g).bfloat16().float()
+        if sl >= 0:
+            pages.write(sl, 0, k, v)
+        qs.append(qq.reshape(t, n_q * d))
+        refs.append(plain_paged_attention(qq, k, v, start, window, scale).reshape(t, n_q * d))
+    q_all = torch.cat(qs).bfloat16().to(DEV)
+    ref = torch.cat(refs)
+    for _ in range(2):                                   # the second launch finds the counters as the first left them
+        out = torch.full(q_all.shape, float("nan"), dtype=torch.bfloat16, device=DEV)
+        assert fast().attention_prefill_tcgen05_bf16(PrefillCtx(seqs), q_all, out, pages.view, n_q, scale)
+        got = out.float().cpu()
+        assert tc_status_clear() == 0
+        o = 0
+        for sl, start, t in seqs:
+            if sl < 0:
+                assert torch.isnan(got[o:o + t]).all()
+            else:
+                assert rel_err(got[o:o + t], ref[o:o + t]) < 1e-2, (sl, start, t)
+            o += t
+
+
+def test_attention_prefill_tcgen05_more_sequences_than_its_table_holds():
+    """Above 512 sequences the kernel reads the sequences' numbers from global memory instead of
+    its shared-memory table."""
+    n_q, n_kv, d = 2, 1, 64
+    seqs = [(i, 0, 1 + i % 3) for i in range(530)] + [(530, 7, 131)]
+    pages = Pages(531, 192, n_kv, d, torch.bfloat16, seed=9)
+    g = gen(31)
+    scale = 1.0 / math.sqrt(d)
+    qs, refs = [], []
+    for sl, start, t in seqs:
+        n = start + t
+        k = torch.randn(n, n_kv, d, generator=g).bfloat16().float()
+        v = torch.randn(n, n_kv, d, generator=g).bfloat16().float()
+        qq = torch.randn(t, n_q, d, generator=g).bfloat16().float()
+        pages.write(sl, 0, k, v)
+        qs.append(qq.reshape(t, n_q * d))
+        refs.append(plain_paged_attention(qq, k, v, start, None, scale).reshape(t, n_q * d))
+    q_all = torch.cat(qs).bfloat16().to(DEV)
+    out = torch.full(q_all.shape, float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert fast().attention_prefill_tcgen05_bf16(PrefillCtx(seqs), q_all, out, pages.view, n_q, scale)
+    assert tc_status_clear() == 0
+    assert rel_err(out.float().cpu(), torch.cat(refs)) < 1e-2
 
 
 def test_attention_prefill_tcgen05_rising_scores():

@@ -311,10 +311,11 @@ __global__ void qk_norm_rope_cache_kernel(T* __restrict__ qkv, long token_stride
 }
 
 // The same for bfloat16 heads of 64 or 128 values with the rotation over the whole head: a lane
-// owns 8 consecutive values (16-byte accesses) and its rotation partner sits half a head away in
-// lane ^ (LANES/2), so nothing goes through shared memory.  LANES = head_dim / 8 lanes per head; a
-// warp handles QKV_UNROLL * 32 / LANES consecutive heads of one token, whose position, page and
-// rotation factors it fetches once.
+// owns 4 consecutive values of the head's first half and the 4 values half a head further on, which
+// are their rotation partners (two 8-byte accesses per head), so the rotation needs no other lane
+// and nothing goes through shared memory.  LANES = head_dim / 8 lanes per head; a warp handles
+// QKV_UNROLL * 32 / LANES consecutive heads of one token, whose position, page and rotation
+// factors it fetches once.
 // QKV_UNROLL: heads a lane group handles, their loads in flight together (1 for few tokens, where
 // more warps matter more)
 template <int D, int QKV_UNROLL>
@@ -326,7 +327,8 @@ qk_norm_rope_cache_vec_kernel(bf16* __restrict__ qkv, long token_stride, int n_t
                               bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, const int* __restrict__ block_table,
                               int table_stride, int flags, int* status) {
     pdl_trigger();
-    constexpr int LANES = D / 8;                        // a lane owns 8 consecutive values (16 bytes)
+    constexpr int LANES = D / 8;                        // a lane owns 4 + 4 values
+    constexpr int HALF = D / 2;
     constexpr int PER_WARP = 32 / LANES;
     constexpr int HPW = PER_WARP * QKV_UNROLL;          // consecutive heads of one token per warp
     const int lane = threadIdx.x & 31, sub = lane % LANES;
@@ -336,44 +338,47 @@ qk_norm_rope_cache_vec_kernel(bf16* __restrict__ qkv, long token_stride, int n_t
     if (item >= (long)n_tokens * groups) return;
     const int t = (int)(item / groups);
     const int head_base = (int)(item - (long)t * groups) * HPW + lane / LANES;
-    bf16* row = qkv + (size_t)t * token_stride + sub * 8;
+    bf16* row = qkv + (size_t)t * token_stride + sub * 4;
 
     const int slot = token_slot[t];
     const int pos = token_pos[t];
     if (slot < 0) return;
     const bool has_rope = rope_table != nullptr;
     const bool bad_pos = has_rope && (pos < 0 || pos >= table_positions);
-    // rotation factors and norm weights of this lane's 8 values, as whole 16-byte loads
-    float2 cs[8];
-    float wq[8], wk[8];
+    // rotation factors of this lane's 4 pairs and the norm weights of its 8 values, as vector loads
+    float2 cs[4];
+    float wq[8], wk[8];                                 // [0..3] first half, [4..7] second half
     if (has_rope && !bad_pos) {
-        const float4* src = reinterpret_cast<const float4*>(rope_table + (size_t)pos * (D / 2) + (sub % (LANES / 2)) * 8);
+        const float4* src = reinterpret_cast<const float4*>(rope_table + (size_t)pos * HALF + sub * 4);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < 2; ++j) {
             const float4 t4 = src[j];
             cs[2 * j] = make_float2(t4.x, t4.y);
             cs[2 * j + 1] = make_float2(t4.z, t4.w);
         }
     } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) cs[j] = make_float2(1.0f, 0.0f);
+        for (int j = 0; j < 4; ++j) cs[j] = make_float2(1.0f, 0.0f);
     }
+    auto unpack4 = [](uint2 raw, float* dst) {
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+        dst[0] = __low2float(a), dst[1] = __high2float(a), dst[2] = __low2float(b), dst[3] = __high2float(b);
+    };
     auto load_w8 = [&](const void* w, float (&dst)[8]) {
         if (w == nullptr) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) dst[j] = 1.0f;
-        } else if (norm_dtype == BFI_BF16 && ((uintptr_t)w & 15) == 0) {
-            const uint4 raw8 = reinterpret_cast<const uint4*>(w)[sub];
-            const uint32_t words[4] = {raw8.x, raw8.y, raw8.z, raw8.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const __nv_bfloat162 two = *reinterpret_cast<const __nv_bfloat162*>(&words[j]);
-                dst[2 * j] = __low2float(two);
-                dst[2 * j + 1] = __high2float(two);
-            }
+        } else if (norm_dtype == BFI_BF16 && ((uintptr_t)w & 7) == 0) {
+            const bf16* wb = reinterpret_cast<const bf16*>(w) + sub * 4;
+            unpack4(*reinterpret_cast<const uint2*>(wb), dst);
+            unpack4(*reinterpret_cast<const uint2*>(wb + HALF), dst + 4);
         } else {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) dst[j] = load_as_f32(w, norm_dtype, sub * 8 + j);
+            for (int j = 0; j < 4; ++j) {
+                dst[j] = load_as_f32(w, norm_dtype, sub * 4 + j);
+                dst[4 + j] = load_as_f32(w, norm_dtype, HALF + sub * 4 + j);
+            }
         }
     };
     load_w8(q_norm_w, wq);
@@ -383,11 +388,13 @@ qk_norm_rope_cache_vec_kernel(bf16* __restrict__ qkv, long token_stride, int n_t
     // the token's slot, position, page, rotation factors and the norm weights were all there before this
     // step's kernels began; only the heads themselves come from the kernel before this one
     pdl_wait();
-    uint4 raw[QKV_UNROLL];
+    uint2 raw_lo[QKV_UNROLL], raw_hi[QKV_UNROLL];
 #pragma unroll
     for (int u = 0; u < QKV_UNROLL; ++u) {
         const int hh = head_base + u * PER_WARP;
-        raw[u] = hh < heads ? *reinterpret_cast<const uint4*>(row + (size_t)hh * D) : make_uint4(0u, 0u, 0u, 0u);
+        const bool live = hh < heads;
+        raw_lo[u] = live ? *reinterpret_cast<const uint2*>(row + (size_t)hh * D) : make_uint2(0u, 0u);
+        raw_hi[u] = live ? *reinterpret_cast<const uint2*>(row + (size_t)hh * D + HALF) : make_uint2(0u, 0u);
     }
     if (bad_pos) {
         if (lane == 0 && status) atomicOr(status, BFI_STATUS_BAD_POSITION);
@@ -401,50 +408,50 @@ qk_norm_rope_cache_vec_kernel(bf16* __restrict__ qkv, long token_stride, int n_t
         const int hh = head_base + u * PER_WARP;
         const bool live = hh < heads;
         const int kind = hh < n_q ? 0 : (hh < n_q + n_kv ? 1 : 2);
-        const uint32_t words[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
-        float v[8];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const __nv_bfloat162 two = *reinterpret_cast<const __nv_bfloat162*>(&words[j]);
-            v[2 * j] = __low2float(two);
-            v[2 * j + 1] = __high2float(two);
-        }
+        uint2 out_lo = raw_lo[u], out_hi = raw_hi[u];
         const bool normed = kind == 0 ? q_norm_w != nullptr : (kind == 1 && k_norm_w != nullptr);
-        float ss = 0.0f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
-#pragma unroll
-        for (int o = LANES / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (normed) {
-            const float scale = 1.0f / sqrtf(ss / (float)D + eps);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = v[j] * scale * (kind == 0 ? wq[j] : wk[j]);
-        }
         const bool rotate = kind != 2 && has_rope;
-        float o8[8];
+        // a warp's lane groups may hold heads of different kinds: the shuffles are run by all lanes
+        // or by none (value heads, which are only copied, mostly fill warps of their own)
+        float v[8];
+        float ss = 0.0f;
+        if (__any_sync(0xffffffffu, normed || rotate)) {
+            unpack4(raw_lo[u], v);
+            unpack4(raw_hi[u], v + 4);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const float other = __shfl_xor_sync(0xffffffffu, v[j], LANES / 2);
-            o8[j] = v[j];
-            if (rotate) o8[j] = sub < LANES / 2 ? v[j] * cs[j].x - other * cs[j].y : other * cs[j].y + v[j] * cs[j].x;
+            for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+#pragma unroll
+            for (int o = LANES / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
         }
-        if (!live) continue;
-        uint4 packed;
-        {
+        if (normed || rotate) {
+            if (normed) {
+                const float scale = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = v[j] * scale * (kind == 0 ? wq[j] : wk[j]);
+            }
+            float o8[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                o8[j] = rotate ? v[j] * cs[j].x - v[4 + j] * cs[j].y : v[j];
+                o8[4 + j] = rotate ? v[4 + j] * cs[j].x + v[j] * cs[j].y : v[4 + j];
+            }
             __nv_bfloat162 p0 = __floats2bfloat162_rn(o8[0], o8[1]), p1 = __floats2bfloat162_rn(o8[2], o8[3]);
             __nv_bfloat162 p2 = __floats2bfloat162_rn(o8[4], o8[5]), p3 = __floats2bfloat162_rn(o8[6], o8[7]);
-            packed.x = *reinterpret_cast<uint32_t*>(&p0);
-            packed.y = *reinterpret_cast<uint32_t*>(&p1);
-            packed.z = *reinterpret_cast<uint32_t*>(&p2);
-            packed.w = *reinterpret_cast<uint32_t*>(&p3);
+            out_lo = make_uint2(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1));
+            out_hi = make_uint2(*reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
         }
+        if (!live) continue;
         const bool in_place = kind == 0 || (kind == 1 && (flags & 2));
-        if (in_place && (normed || rotate)) *reinterpret_cast<uint4*>(row + (size_t)hh * D) = packed;
+        if (in_place && (normed || rotate)) {
+            *reinterpret_cast<uint2*>(row + (size_t)hh * D) = out_lo;
+            *reinterpret_cast<uint2*>(row + (size_t)hh * D + HALF) = out_hi;
+        }
         if (kind != 0 && (flags & 1) && page >= 0) {
             bf16* pages = kind == 1 ? k_pages : v_pages;
             const int h = kind == 1 ? hh - n_q : hh - n_q - n_kv;
-            bf16* dst = pages + (((size_t)page * n_kv + h) * BFI_PAGE_TOKENS + (pos % BFI_PAGE_TOKENS)) * D + sub * 8;
-            *reinterpret_cast<uint4*>(dst) = packed;
+            bf16* dst = pages + (((size_t)page * n_kv + h) * BFI_PAGE_TOKENS + (pos % BFI_PAGE_TOKENS)) * D + sub * 4;
+            *reinterpret_cast<uint2*>(dst) = out_lo;
+            *reinterpret_cast<uint2*>(dst + HALF) = out_hi;
         }
     }
 }

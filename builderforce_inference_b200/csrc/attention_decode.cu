@@ -270,6 +270,31 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
     const int n_splits = (n_pages + pps - 1) / pps;
     if (n_splits == 1) return;                            // the first kernel wrote the output itself
     const size_t base = ((size_t)seq * n_q + head) * max_splits;
+    if (n_splits <= 8) {
+        // few ranges: every load of this thread is issued before the first is used, so the kernel
+        // costs one trip to memory after its wait instead of three
+        float ms[8], ls[8], os[8];
+        const int e = threadIdx.x;                        // blockDim.x == D here
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            const bool have = s < n_splits;
+            ms[s] = have ? part_ml[(base + s) * 2] : -INFINITY;
+            ls[s] = have ? part_ml[(base + s) * 2 + 1] : 0.0f;
+            os[s] = have ? part_o[(base + s) * D + e] : 0.0f;
+        }
+        float m = ms[0];
+#pragma unroll
+        for (int s = 1; s < 8; ++s) m = fmaxf(m, ms[s]);
+        float l = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            const float f = (ms[s] == -INFINITY) ? 0.0f : fast_exp2(ms[s] - m);
+            l += ls[s] * f;
+            acc = fmaf(os[s], f, acc);
+        }
+        out[(size_t)seq * out_stride + (size_t)head * D + e] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+        return;
+    }
     float m = -INFINITY;
     for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
     float l = 0.0f;
@@ -312,7 +337,7 @@ static int launch_decode(const void* q, long q_stride, void* out, long out_strid
                scale_log2, head_chunks, part_o, part_ml);
     int rc = bfi_check_launch("attention_decode");
     if (rc || max_splits == 1) return rc;
-    bfi_launch(attention_decode_merge_kernel<D>, dim3(n_q, n_seqs), dim3(D <= 64 ? 64 : 128), 0, stream,
+    bfi_launch(attention_decode_merge_kernel<D>, dim3(n_q, n_seqs), dim3(D), 0, stream,
                (const float*)part_o, (const float*)part_ml, seq_slot, seq_start, (bf16*)out, out_stride, n_q, max_splits,
                window);
     return bfi_check_launch("attention_decode_merge");

@@ -92,6 +92,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    float c_pre0 = 0.0f, c_pre1 = 0.0f, c_pre2 = 0.0f, c_pre3 = 0.0f;     // epilogue threads: see there
 
     if (warp == 0) {
         // ---------------- TMA producer
@@ -158,6 +159,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const int n_local = quad * 32 + lane;
         const int n = n0 + n_local;
         bool ok = true;
+        if (ksplit > 1 && epilogue == EPI_ACCUMULATE && n < N) {
+            // the values this thread will add to (no kernel in flight writes them any more) are
+            // fetched now, while the products run, instead of behind them
+            const int per_rank = (BT + ksplit - 1) / ksplit;
+            const int j0 = (int)blockIdx.z * per_rank;
+            const float* c_in = reinterpret_cast<const float*>(C);
+            if (0 < per_rank && j0 + 0 < BT && m0 + j0 + 0 < M) c_pre0 = c_in[(size_t)(m0 + j0 + 0) * ldc + n];
+            if (1 < per_rank && j0 + 1 < BT && m0 + j0 + 1 < M) c_pre1 = c_in[(size_t)(m0 + j0 + 1) * ldc + n];
+            if (2 < per_rank && j0 + 2 < BT && m0 + j0 + 2 < M) c_pre2 = c_in[(size_t)(m0 + j0 + 2) * ldc + n];
+            if (3 < per_rank && j0 + 3 < BT && m0 + j0 + 3 < M) c_pre3 = c_in[(size_t)(m0 + j0 + 3) * ldc + n];
+        }
         if (n_kb > 0) {
             ok = mbar_wait(tmem_full, 0);
             if (!ok && lane == 0) {
@@ -245,10 +257,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         store_from_f32(C, c_dtype, (size_t)m * ldc + (n >> 1), silu_mul_tc(v, up));
                 } else if (n < N) {
                     const size_t o = (size_t)m * ldc + n;
-                    if (epilogue == EPI_ACCUMULATE)
-                        reinterpret_cast<float*>(C)[o] += v;
-                    else
+                    if (epilogue == EPI_ACCUMULATE) {
+                        const int jj = j - rank * per_rank;
+                        const float old = jj == 0 ? c_pre0 : jj == 1 ? c_pre1 : jj == 2 ? c_pre2 : jj == 3 ? c_pre3
+                                                                                     : reinterpret_cast<float*>(C)[o];
+                        reinterpret_cast<float*>(C)[o] = old + v;
+                    } else {
                         store_from_f32(C, c_dtype, o, v);
+                    }
                 }
             }
         }

@@ -35,6 +35,8 @@ from ..weights.random_init import random_tensors
 from .context import StepContext, Workspace
 from .decoder import Decoder, Runtime, expected_tensors
 
+PINNED_RING = 4          # pinned staging buffers per size of a step's index arrays
+
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 
 
@@ -120,7 +122,7 @@ class Engine:
         self.prefill_chunk_tokens = max(PAGE_TOKENS, int(prefill_chunk_tokens))
         self.use_graphs = bool(use_graphs) and self.decoder.graph_safe()
         self._graphs: Dict[int, _DecodeGraph] = {}
-        self._pinned: Dict[int, torch.Tensor] = {}
+        self._pinned: Dict[int, dict] = {}
         self.last_h2d_bytes = 0        # bytes of index arrays the last step copied to the device
         self.graph_kernel_launches = 0  # kernels launched through graph replays so far
 
@@ -361,15 +363,24 @@ class Engine:
             i32(cu), np.full(pad_s, last, np.int32), i32(seq_slots), np.full(pad_s, -1, np.int32),
             i32(seq_starts), np.zeros(pad_s, np.int32), i32([pages]), i32(want_rows)])
         n = host.shape[0]
-        pinned = self._pinned.get(n)
-        if pinned is None:
-            pinned = torch.empty(n, dtype=torch.int32, pin_memory=True)
-            self._pinned[n] = pinned
+        # a ring of pinned staging buffers per size: a buffer is rewritten only after the copy that
+        # last read it has completed (its event), which with four in rotation was steps ago, so the
+        # host packs the next step while the GPU still runs this one
+        ring = self._pinned.setdefault(n, {"next": 0, "slots": []})
+        if len(ring["slots"]) < PINNED_RING:
+            ring["slots"].append([torch.empty(n, dtype=torch.int32, pin_memory=True), None])
+            entry = ring["slots"][-1]
         else:
-            # the previous copy from this buffer must have been consumed before it is rewritten
-            torch.cuda.current_stream(self.device).synchronize()
+            entry = ring["slots"][ring["next"]]
+            ring["next"] = (ring["next"] + 1) % PINNED_RING
+            if entry[1] is not None:
+                entry[1].synchronize()
+        pinned = entry[0]
         pinned.numpy()[:] = host
         meta[:n].copy_(pinned, non_blocking=True)
+        if entry[1] is None:
+            entry[1] = torch.cuda.Event()
+        entry[1].record(torch.cuda.current_stream(self.device))
         self.last_h2d_bytes = 4 * n
 
     def _context_from_meta(self, meta, n_tok, n_seq, max_seq_tokens, host) -> StepContext:

@@ -37,6 +37,38 @@ from .decoder import Decoder, Runtime, expected_tensors
 
 PINNED_RING = 4          # pinned staging buffers per size of a step's index arrays
 
+
+def pack_meta(dst: np.ndarray, tok, pos, slot_of, cu, n_tok: int, n_seq: int, seq_slots, seq_starts, pages: int,
+              want_rows=()) -> int:
+    """Write a step's index arrays into ``dst`` (int32) in the layout the kernels read:
+    token_ids[T] token_pos[T] token_slot[T] cu_seqlens[B+1] seq_slot[B] seq_start[B] total_pages[1]
+    want_rows[W], with T = n_tok and B = n_seq; rows and sequences past the real ones are padding
+    (ids and positions 0, slots -1, cu_seqlens repeating the last offset).  Returns the count written."""
+    k, b, last = len(tok), len(seq_slots), cu[-1]
+    o = 0
+    dst[o:o + k] = tok
+    dst[o + k:o + n_tok] = 0
+    o += n_tok
+    dst[o:o + k] = pos
+    dst[o + k:o + n_tok] = 0
+    o += n_tok
+    dst[o:o + k] = slot_of
+    dst[o + k:o + n_tok] = -1
+    o += n_tok
+    dst[o:o + len(cu)] = cu
+    dst[o + len(cu):o + n_seq + 1] = last
+    o += n_seq + 1
+    dst[o:o + b] = seq_slots
+    dst[o + b:o + n_seq] = -1
+    o += n_seq
+    dst[o:o + b] = seq_starts
+    dst[o + b:o + n_seq] = 0
+    o += n_seq
+    dst[o] = pages
+    o += 1
+    dst[o:o + len(want_rows)] = want_rows
+    return o + len(want_rows)
+
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 
 
@@ -351,18 +383,10 @@ class Engine:
         In a single-token step ``pos`` doubles as the sequences' starts and ``slot_of`` as their slots."""
         if seq_slots is None:
             seq_slots, seq_starts = slot_of, pos
-        pad_t = n_tok - len(tok)
-        pad_s = n_seq - len(seq_slots)
-        last = cu[-1]
         # pages the sequences hold after this step, summed: kernels size their work split by it
         pages = sum((int(st) + (int(cu[i + 1]) - int(cu[i])) + PAGE_TOKENS - 1) // PAGE_TOKENS
                     for i, st in enumerate(seq_starts))
-        i32 = lambda xs: np.asarray(xs, dtype=np.int32)
-        host = np.concatenate([
-            i32(tok), np.zeros(pad_t, np.int32), i32(pos), np.zeros(pad_t, np.int32), i32(slot_of), np.full(pad_t, -1, np.int32),
-            i32(cu), np.full(pad_s, last, np.int32), i32(seq_slots), np.full(pad_s, -1, np.int32),
-            i32(seq_starts), np.zeros(pad_s, np.int32), i32([pages]), i32(want_rows)])
-        n = host.shape[0]
+        n = self._meta_len(n_tok, n_seq, len(want_rows))
         # a ring of pinned staging buffers per size: a buffer is rewritten only after the copy that
         # last read it has completed (its event), which with four in rotation was steps ago, so the
         # host packs the next step while the GPU still runs this one
@@ -376,7 +400,7 @@ class Engine:
             if entry[1] is not None:
                 entry[1].synchronize()
         pinned = entry[0]
-        pinned.numpy()[:] = host
+        pack_meta(pinned.numpy(), tok, pos, slot_of, cu, n_tok, n_seq, seq_slots, seq_starts, pages, want_rows)
         meta[:n].copy_(pinned, non_blocking=True)
         if entry[1] is None:
             entry[1] = torch.cuda.Event()

@@ -165,3 +165,31 @@ def test_sample_params_and_draws():
     assert all(0.0 <= u < 1.0 for u in us) and len(set(us)) == len(us)
     assert uniform_draw(3, 1, 2) == uniform_draw(3, 1, 2) != uniform_draw(4, 1, 2)
     assert abs(sum(us) / len(us) - 0.5) < 0.1
+
+
+def test_the_step_index_arrays_are_packed_in_the_layout_the_kernels_read():
+    """``pack_meta`` against the layout written out plainly: ids, positions, slots (padded with 0, 0,
+    -1), cu_seqlens (padded with its last offset), sequence slots and starts (padded with -1 and
+    0), the page count, the wanted rows."""
+    import numpy as np
+    from builderforce_inference_b200.engine.engine import pack_meta
+    rng = np.random.default_rng(5)
+    for n_real_seq, n_seq, pad_tok in ((1, 1, 0), (3, 4, 5), (8, 16, 8), (5, 5, 0)):
+        counts = rng.integers(1, 7, n_real_seq)
+        cu = [0] + list(np.cumsum(counts))
+        k = int(cu[-1])
+        n_tok = k + pad_tok
+        tok = rng.integers(0, 1000, k).tolist()
+        pos = rng.integers(0, 500, k).astype(np.int32)
+        slot_of = rng.integers(0, 9, k).tolist()
+        seq_slots = rng.integers(0, 9, n_real_seq).tolist()
+        seq_starts = rng.integers(0, 400, n_real_seq).tolist()
+        want = rng.integers(0, k, 3).tolist()
+        plain = np.concatenate([
+            tok, np.zeros(pad_tok), pos, np.zeros(pad_tok), slot_of, np.full(pad_tok, -1),
+            cu, np.full(n_seq - n_real_seq, cu[-1]), seq_slots, np.full(n_seq - n_real_seq, -1),
+            seq_starts, np.zeros(n_seq - n_real_seq), [77], want]).astype(np.int32)
+        dst = np.full(plain.shape[0] + 3, 12345, dtype=np.int32)
+        n = pack_meta(dst, tok, pos, slot_of, cu, n_tok, n_seq, seq_slots, seq_starts, 77, want)
+        assert n == plain.shape[0]
+        assert (dst[:n] == plain).all() and (dst[n:] == 12345).all()

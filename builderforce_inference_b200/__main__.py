@@ -17,7 +17,6 @@ import argparse
 import json
 import re
 import sys
-import time
 
 
 def _ids(text: str):

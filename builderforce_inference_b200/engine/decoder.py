@@ -7,13 +7,13 @@ specific arrives in the spec.
 """
 from __future__ import annotations
 
-from typing import Any, Dict, List, Optional, Sequence
+from typing import Any, Dict, List, Optional
 
 import torch
 
 from ..kernels import ops
 from ..kernels.linear import EPI_STORE, linear
-from ..parts.base import BLOCKS, NORMS, Block, KVNeed, ModelSpec, ParamSpec, StateNeed
+from ..parts.base import BLOCKS, NORMS, Block, ModelSpec, ParamSpec
 
 
 class Runtime:

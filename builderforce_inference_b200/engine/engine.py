@@ -15,9 +15,8 @@ skips, so padding changes no result.
 """
 from __future__ import annotations
 
-import json
 import os
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -25,7 +24,7 @@ import torch
 
 from ..cache.cache import SequenceCache
 from ..cache.pages import PAGE_TOKENS, CacheError
-from ..config.base import ConfigError, read_json
+from ..config.base import read_json
 from ..kernels import ops
 from ..kernels.library import total_calls
 from ..parts.base import ModelSpec

@@ -3,7 +3,7 @@ take the shape (the caller then uses the general kernel); it never computes a wr
 """
 from __future__ import annotations
 
-from ctypes import c_float, c_int, c_long, c_void_p
+from ctypes import c_float, c_int, c_long
 
 import torch
 

@@ -5,7 +5,6 @@ Nothing here computes anything, and nothing falls back to another implementation
 """
 from __future__ import annotations
 
-import ctypes
 from ctypes import c_float, c_int, c_long, c_void_p
 from typing import Optional
 

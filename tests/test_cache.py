@@ -5,7 +5,7 @@ import random
 import pytest
 import torch
 
-from builderforce_inference_b200.cache import PAGE_TOKENS, CacheError, FreeList, PageTable, SequenceCache
+from builderforce_inference_b200.cache import PAGE_TOKENS, CacheError, FreeList, SequenceCache
 from builderforce_inference_b200.parts.base import KVNeed, StateNeed
 
 CPU = torch.device("cpu")

@@ -43,23 +43,38 @@ class KVView:
 
 @dataclass
 class RunCache:
-    """The cache of one run of the schedule, as handed to its mixer."""
+    """The cache of one run of the schedule, as handed to its mixer.  A mixer that declared
+    several needs finds one entry per need, in the order it declared them, in ``entries``
+    (a ``KVView`` for a ``KVNeed``, a ``[slots, *shape]`` tensor for a ``StateNeed``); ``kv`` and
+    ``state`` are the first entry of each sort."""
 
     kv: Optional[KVView] = None
     state: Optional[torch.Tensor] = None   # [slots, *shape]
     writes_cache: bool = True
+    entries: tuple = ()
+
+
+def needs_of(need) -> tuple:
+    """What a mixer's ``cache_need()`` returned, as a tuple of needs: it may name none, one, or
+    several (keys and values beside a fixed-size state, for instance)."""
+    if need is None:
+        return ()
+    if isinstance(need, (KVNeed, StateNeed)):
+        return (need,)
+    return tuple(need)
 
 
 class _KVGroup:
-    def __init__(self, need: KVNeed, runs: List[int], n_pages: int, n_slots: int, n_blocks: int,
+    def __init__(self, need: KVNeed, keys: List[Any], n_pages: int, n_slots: int, n_blocks: int,
                  dtype: torch.dtype, device: torch.device):
         self.need = need
-        self.runs = runs
+        self.keys = keys                       # (run, index among the run's needs) per place
+        self.runs = [r for r, _ in keys]
         self.table = PageTable(n_pages, need.window)
         self.n_blocks = n_blocks
         self.device = device
         self.storage = torch.empty(
-            (len(runs), 2, n_pages, need.n_kv_heads, PAGE_TOKENS, need.head_dim),
+            (len(keys), 2, n_pages, need.n_kv_heads, PAGE_TOKENS, need.head_dim),
             dtype=dtype, device=device)
         self._alloc_tables(n_slots)
 
@@ -85,8 +100,8 @@ class _KVGroup:
             host[:len(row)] = torch.tensor(row, dtype=torch.int32)
         self.block_dev[slot].copy_(host)
 
-    def view(self, run: int) -> KVView:
-        i = self.runs.index(run)
+    def view(self, key) -> KVView:
+        i = self.keys.index(key)
         return KVView(k=self.storage[i, 0], v=self.storage[i, 1], block_table=self.block_dev,
                       n_kv_heads=self.need.n_kv_heads, head_dim=self.need.head_dim,
                       window=self.need.window)
@@ -96,13 +111,14 @@ class _KVGroup:
 
 
 class _StateGroup:
-    def __init__(self, need: StateNeed, runs: List[int], n_slots: int, device: torch.device):
+    def __init__(self, need: StateNeed, keys: List[Any], n_slots: int, device: torch.device):
         self.need = need
-        self.runs = runs
+        self.keys = keys
+        self.runs = [r for r, _ in keys]
         self.device = device
         self.dtype = _TORCH_DTYPES[need.dtype]
-        self.storage = {r: torch.zeros((n_slots,) + tuple(need.shape), dtype=self.dtype, device=device)
-                        for r in runs}
+        self.storage = {k: torch.zeros((n_slots,) + tuple(need.shape), dtype=self.dtype, device=device)
+                        for k in keys}
 
     def grow_slots(self, n_slots: int) -> None:
         for r, old in list(self.storage.items()):
@@ -148,38 +164,41 @@ class SequenceCache:
         self.cache_of = list(cache_of)
         self.kv_groups: List[_KVGroup] = []
         self.state_groups: List[_StateGroup] = []
-        self._owner: Dict[int, Any] = {}     # run -> its group
-        by_need: Dict[Any, List[int]] = {}
+        self._owner: Dict[int, List[Any]] = {}     # run -> [(need index, group, key in the group)]
+        by_need: Dict[Any, List[Any]] = {}
         for run, need in enumerate(needs):
             if self.cache_of[run] is not None:
                 src = self.cache_of[run]
                 if not 0 <= src < run or self.cache_of[src] is not None:
                     raise CacheError(f"run {run} reads the cache of run {src}, which keeps none of its own")
                 continue
-            if need is not None:
-                by_need.setdefault(need, []).append(run)
-        for need, runs in by_need.items():
+            self._owner[run] = []
+            for j, one in enumerate(needs_of(need)):
+                # a run that names the same need twice gets two places in that need's group
+                by_need.setdefault(one, []).append((run, j))
+        for need, keys in by_need.items():
             if isinstance(need, KVNeed):
-                g = _KVGroup(need, runs, self.n_pages, n_slots, self.n_blocks, dtype, self.device)
+                g = _KVGroup(need, keys, self.n_pages, n_slots, self.n_blocks, dtype, self.device)
                 self.kv_groups.append(g)
             elif isinstance(need, StateNeed):
-                g = _StateGroup(need, runs, n_slots, self.device)
+                g = _StateGroup(need, keys, n_slots, self.device)
                 self.state_groups.append(g)
             else:
                 raise CacheError(f"unknown cache need {need!r}")
-            for r in runs:
-                self._owner[r] = g
+            for key in keys:
+                self._owner[key[0]].append((key[1], g, key))
+        for own in self._owner.values():
+            own.sort(key=lambda e: e[0])           # the order in which the mixer declared its needs
 
     # ---- what a run sees -------------------------------------------------------------
     def run_cache(self, run: int) -> RunCache:
         src = self.cache_of[run]
         owner_run = run if src is None else src
-        g = self._owner.get(owner_run)
-        if g is None:
-            return RunCache(writes_cache=src is None)
-        if isinstance(g, _KVGroup):
-            return RunCache(kv=g.view(owner_run), writes_cache=src is None)
-        return RunCache(state=g.storage[owner_run], writes_cache=src is None)
+        entries = tuple(g.view(key) if isinstance(g, _KVGroup) else g.storage[key]
+                        for _, g, key in self._owner.get(owner_run, ()))
+        kv = next((e for e in entries if isinstance(e, KVView)), None)
+        state = next((e for e in entries if not isinstance(e, KVView)), None)
+        return RunCache(kv=kv, state=state, writes_cache=src is None, entries=entries)
 
     # ---- slots -----------------------------------------------------------------------
     def acquire(self) -> int:
@@ -253,6 +272,30 @@ class SequenceCache:
             for s in slots:
                 if g.table.trim(s, self.lengths[s]):
                     g.sync_row(s)
+
+    def rewind(self, slot: int, length: int) -> None:
+        """Keep only the first ``length`` tokens of ``slot``: its fill mark moves back and the pages
+        past it return to the pool (crates/bfi-models/src/session.rs:50-62).  Only a cache that
+        keeps every key can do that: a windowed group has already let go of pages the shorter
+        sequence would read, and a fixed-size state cannot be wound back at all, so a model with
+        either refuses by name and changes nothing."""
+        if slot not in self.lengths:
+            raise CacheError(f"slot {slot} is not held")
+        if not 0 <= length <= self.lengths[slot]:
+            raise CacheError(f"rewind: slot {slot} holds {self.lengths[slot]} tokens, cannot keep {length}")
+        if length == self.lengths[slot]:
+            return
+        if self.state_groups:
+            raise CacheError("rewind unsupported: the model keeps per-sequence state of fixed size, "
+                             "which cannot be wound back; release the slot and start again")
+        windowed = [g.need.window for g in self.kv_groups if g.need.window is not None]
+        if windowed:
+            raise CacheError(f"rewind unsupported: layers with a window of {windowed[0]} keys have given "
+                             "back pages the shorter sequence would read; release the slot and start again")
+        for g in self.kv_groups:
+            if g.table.shrink(slot, length):
+                g.sync_row(slot)
+        self.lengths[slot] = length
 
     # ---- accounting and checks -------------------------------------------------------
     def bytes_per_token(self) -> int:

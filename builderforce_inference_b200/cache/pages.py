@@ -129,6 +129,21 @@ class PageTable:
                 changed = True
         return changed
 
+    def shrink(self, slot: int, length: int) -> bool:
+        """Give back pages that hold no position below ``length`` (the sequence is cut back to its
+        first ``length`` tokens).  Returns True if the row changed."""
+        row = self.rows[slot]
+        keep = (length + PAGE_TOKENS - 1) // PAGE_TOKENS
+        changed = False
+        for b in range(keep, len(row)):
+            if row[b] >= 0:
+                self.pool.give_back(row[b])
+                changed = True
+        if len(row) > keep:
+            del row[keep:]
+            changed = True
+        return changed
+
     def close(self, slot: int) -> None:
         row = self.rows.pop(slot, None)
         if row is None:

@@ -192,3 +192,88 @@ def test_random_traffic_never_loses_or_duplicates_anything():
     for g in c.kv_groups:
         assert g.table.held_pages() == 0 and g.table.pool.n_free == g.table.pool.capacity
     assert c.slots.n_held == 0
+
+
+def test_rewind_gives_pages_back_and_refuses_what_cannot_be_wound_back():
+    c = make(max_tokens=64 * 8, max_seq_len=512)
+    a, b = c.acquire(), c.acquire()
+    c.begin_step([a, b], [200, 70]); c.end_step([a, b], [200, 70])
+    g = c.kv_groups[0]
+    assert g.table.held_pages() == 4 + 2
+    kept = list(g.table.rows[a][:2])
+    c.rewind(a, 100)                                   # session.rs:53-62: the fill mark moves back
+    assert c.length(a) == 100 and g.table.rows[a] == kept and g.table.held_pages() == 2 + 2
+    assert g.block_host[a, :4].tolist() == kept + [-1, -1]
+    c.rewind(a, 100)                                   # nothing to do
+    with pytest.raises(CacheError, match="cannot keep"):
+        c.rewind(a, 101)
+    with pytest.raises(CacheError, match="not held"):
+        c.rewind(7, 0)
+    c.begin_step([a], [130]); c.end_step([a], [130])   # grows again over the freed pages
+    assert c.length(a) == 230 and g.table.held_pages() == 4 + 2
+    c.rewind(b, 0)
+    assert c.length(b) == 0 and g.table.rows[b] == []
+    c.check()
+    w = make(needs=[KVNeed(1, 16), KVNeed(1, 16, window=40)], max_seq_len=512)
+    s = w.acquire()
+    w.begin_step([s], [100]); w.end_step([s], [100])
+    with pytest.raises(CacheError, match="rewind unsupported.*window of 40"):
+        w.rewind(s, 50)
+    assert w.length(s) == 100
+    st = make(needs=[KVNeed(1, 16), StateNeed((4,))])
+    s = st.acquire()
+    st.begin_step([s], [10]); st.end_step([s], [10])
+    with pytest.raises(CacheError, match="rewind unsupported.*fixed size"):
+        st.rewind(s, 5)
+    st.rewind(s, 10)
+    st.check()
+
+
+def test_a_run_may_declare_several_needs():
+    """Keys and values AND a fixed-size state for one mixer; the same need twice gives two places."""
+    both = (KVNeed(2, 16), StateNeed((3,)))
+    needs = [both, KVNeed(2, 16), (StateNeed((3,)), StateNeed((3,)), StateNeed((5,), "int32")), both]
+    c = make(needs=needs, cache_of=[None, None, None, 0])
+    assert [g.keys for g in c.kv_groups] == [[(0, 0), (1, 0)]]
+    assert [g.keys for g in c.state_groups] == [[(0, 1), (2, 0), (2, 1)], [(2, 2)]]
+    r0, r2, r3 = c.run_cache(0), c.run_cache(2), c.run_cache(3)
+    assert isinstance(r0.entries[0], type(r0.kv)) and r0.entries[1] is r0.state and r0.state.shape[1:] == (3,)
+    assert r0.kv is not None and r0.kv.k.data_ptr() != c.run_cache(1).kv.k.data_ptr()
+    assert len(r2.entries) == 3 and r2.kv is None and r2.entries[0].data_ptr() != r2.entries[1].data_ptr()
+    assert r2.entries[2].dtype == torch.int32 and r2.entries[2].shape[1:] == (5,)
+    assert r3.kv.k.data_ptr() == r0.kv.k.data_ptr() and r3.state.data_ptr() == r0.state.data_ptr()
+    assert not r3.writes_cache
+    a = c.acquire()
+    r2.entries[1][a] += 2.0
+    c.release(a)
+    assert c.acquire() == a and c.run_cache(2).entries[1][a].abs().sum() == 0
+    assert c.bytes_per_token() == 2 * 2 * 2 * 16 * 4
+    assert c.state_bytes_per_slot() == (3 + 3 + 3) * 4 + 5 * 4
+
+
+def test_cache_sized_from_a_byte_budget():
+    from builderforce_inference_b200.cache import plan_cache, served_context
+    # the reference's own predictions (kv_plan.rs:166-176): 36 / 28 layers, 8 kv heads of 128
+    gib2, binding = 2 << 30, 128 << 20
+    assert served_context(36, 8, 128, 2, gib2, 65536, binding) == 14336
+    assert served_context(36, 8, 128, 4, gib2, 65536, binding) == 7168
+    assert served_context(28, 8, 128, 2, gib2, 32768, binding) == 18688
+    assert served_context(28, 8, 128, 4, gib2, 32768, binding) == 9216
+    assert served_context(28, 8, 128, 2, 1 << 62, 4096, None) == 4096           # kv_plan.rs:180-181
+    assert served_context(36, 8, 128, 2, 1 << 62, 65536, 1 << 20) == 512        # kv_plan.rs:183
+    needs = [KVNeed(8, 128)] * 36
+    p = plan_cache(needs, [None] * 36, gib2, 2)
+    assert p.bytes_per_token == 147456 and p.max_tokens == 14336 and p.kv_bytes <= gib2
+    # fixed-size state comes off the budget first; a run that reads another's cache costs nothing
+    needs = [(KVNeed(2, 16), StateNeed((100,))), KVNeed(2, 16, window=8), KVNeed(2, 16)]
+    p = plan_cache(needs, [None, None, 0], 1_000_000, 4, n_slots=10)
+    assert p.state_bytes_per_slot == 400 and p.bytes_per_token == 2 * (2 * 2 * 16 * 4)
+    assert p.max_tokens == (1_000_000 - 4000) // 512 // 256 * 256 == 1792
+    assert p.kv_bytes + p.state_bytes <= 1_000_000
+    assert plan_cache(needs, [None, None, 0], 4000 + 512 * 200, 4, n_slots=10).max_tokens == 192
+    with pytest.raises(CacheError, match="holds no page"):
+        plan_cache(needs, [None, None, 0], 4000 + 512 * 63, 4, n_slots=10)
+    # the plan is what a cache of that size really allocates
+    c = SequenceCache(needs, [None, None, 0], p.max_tokens, 256, torch.float32, CPU, initial_slots=10)
+    assert sum(g.storage.numel() * 4 for g in c.kv_groups) == p.kv_bytes
+    assert c.bytes_per_token() == p.bytes_per_token and c.state_bytes_per_slot() == p.state_bytes_per_slot

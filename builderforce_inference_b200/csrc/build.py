@@ -24,7 +24,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 # the bfloat16 path.  "fast": the bfloat16 kernels written for the tensor cores and for
 # streaming weights and the cache at memory speed.
 LIBRARIES: Dict[str, List[str]] = {
-    "core": ["errors.cu", "elementwise.cu", "gemm_simt.cu", "attention_paged.cu", "sampling.cu"],
+    "core": ["errors.cu", "elementwise.cu", "gemm_simt.cu", "attention_paged.cu", "sampling.cu", "utility.cu"],
     "fast": ["errors.cu", "skinny_gemm.cu", "attention_decode.cu", "attention_prefill.cu", "gemm_tcgen05.cu",
              "attention_prefill_tcgen05.cu"],
 }

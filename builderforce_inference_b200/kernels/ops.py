@@ -63,6 +63,18 @@ def _i32(t: Optional[torch.Tensor], what: str) -> None:
         raise KernelError(f"{what} must be a contiguous int32 tensor")
 
 
+def convert(src: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """A contiguous copy of ``src`` (float32 or bfloat16, on the GPU) in ``dtype``; rounding to
+    bfloat16 is to nearest even."""
+    _need_cuda(src)
+    src = src.contiguous()
+    out = torch.empty(src.shape, dtype=dtype, device=src.device)
+    with torch.cuda.device(src.device):
+        library("core").call("bfi_convert", _ptr(src), c_int(dtype_code(src.dtype)), _ptr(out),
+                             c_int(dtype_code(dtype)), c_long(src.numel()), _stream())
+    return out
+
+
 def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor,
                status: Optional[torch.Tensor] = None) -> None:
     _need_cuda(table, ids, out, status)

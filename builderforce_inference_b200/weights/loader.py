@@ -114,7 +114,13 @@ def load_folder(folder: str, expected: Mapping[str, ParamSpec], ignored: Iterabl
             continue
         host = where[n].tensor(n)
         keep = stored_dtype_for(run_dtype, host.dtype)
-        out[n] = host.to(device=device, dtype=keep).contiguous()
+        both = (torch.float32, torch.bfloat16)
+        if torch.device(device).type == "cuda" and host.dtype != keep and host.dtype in both and keep in both:
+            # widened (or narrowed) on the device by the library's own conversion kernel
+            from ..kernels import ops
+            out[n] = ops.convert(host.to(device=device), keep)
+        else:
+            out[n] = host.to(device=device, dtype=keep).contiguous()
     for f in set(where.values()):
         f.close()
     return out

@@ -148,3 +148,22 @@ def test_random_weights_depend_on_seed_and_name_only():
     write_model_folder(TINY_A, 5, d, torch.float32)
     assert sorted(os.listdir(d)) == ["config.json", "model.safetensors"]
     assert json.load(open(os.path.join(d, "config.json")))["vocab_size"] == 256
+
+
+def test_random_fill_is_the_closed_formula_bit_for_bit():
+    """The product's numpy fill against the plain restatement in Python integers, float32 and
+    bfloat16, for matrices and norm weights, at scattered indices of a large tensor too."""
+    from plain import random_fill_plain as R
+    from builderforce_inference_b200.parts.base import ParamSpec
+    from builderforce_inference_b200.weights.random_init import random_tensor
+    for role, shape in (("matrix", (37, 53)), ("norm", (301,)), ("table", (70001, 3))):
+        t = random_tensor("some.tensor", ParamSpec(shape, role), 9, torch.float32, CPU).reshape(-1)
+        tb = random_tensor("some.tensor", ParamSpec(shape, role), 9, torch.bfloat16, CPU).reshape(-1)
+        n = t.numel()
+        for i in sorted({0, 1, 2, 63, 64, n // 3, 65535 % n, 65536 % n, n - 2, n - 1}):
+            want = R.value(9, "some.tensor", i, role)
+            assert float(t[i]) == want, (role, i)
+            assert int(tb[i].view(torch.int16)) & 0xFFFF == R.bf16_bits(want), (role, i)
+    big = random_tensor("w", ParamSpec((1000, 1000)), 3, torch.float32, CPU)
+    assert abs(float(big.std()) - 0.02) < 2e-4 and abs(float(big.mean())) < 1e-4
+    assert float(big.abs().max()) <= 0.02 * 4.9

@@ -117,9 +117,9 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 // of the warp writes four whole 128-byte lines instead of 16 bytes of 32 different rows.
 template <int D>
 __device__ __noinline__ bool ft_write_out(uint64_t* o_done, uint32_t parity, uint64_t* o_free, uint32_t o_addr, float l_sum,
-                                          bf16* dst, long out_stride, int rows_here, uint32_t stage) {
+                                          bf16* dst, long out_stride, int rows_here, uint32_t stage, uint32_t spin_limit) {
     const int lane = threadIdx.x & 31;
-    if (!__all_sync(0xffffffffu, mbar_wait(o_done, parity))) return false;
+    if (!__all_sync(0xffffffffu, MBAR_WAIT(o_done, parity))) return false;
     tc_fence_after();
     const float inv = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
     float o[D];
@@ -176,7 +176,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_seqlens,
                             const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int n_seqs, int max_tiles,
                             int n_q, int n_kv, int window, float scale_log2, uint32_t v_lbo, uint32_t v_sbo,
-                            int* __restrict__ status, int* __restrict__ counters) {
+                            int* __restrict__ status, int* __restrict__ counters, TcWaits waits) {
+    const uint32_t spin_limit = waits.spin_limit;
     constexpr int BOXES = D / 64;
     constexpr int TILE_BYTES = BOXES * FT_BOX_BYTES;       // a Q tile, a K tile or a V tile
     constexpr int PAGE_BYTES = FT_PAGE * 128;              // one page's rows inside a box
@@ -247,7 +248,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     pdl_trigger();
     pdl_wait();
 
-    if (warp == 4) {
+    if (warp == 4 && waits.hold_producer) {
+        // the probe of the time-out path: no item is drawn and no copy issued, so every other role's
+        // first wait runs out
+    } else if (warp == 4) {
         // ---------------------------------------------------------------- TMA producer
         const int per_level = n_seqs * n_q;
         const int total = max_tiles * per_level;
@@ -300,7 +304,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const int qi = it & 1;
             int ok = 1;
             if (lane == 0) {
-                if (it >= 2 && !mbar_wait(&q_empty[qi], ((uint32_t)(it >> 1) & 1) ^ 1)) ok = 0;
+                if (it >= 2 && !MBAR_WAIT(&q_empty[qi], ((uint32_t)(it >> 1) & 1) ^ 1)) ok = 0;
                 if (ok && !p.have) {
                     items[qi].n_tiles = 0;
                     mbar_arrive(&q_full[qi]);
@@ -341,7 +345,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 unsigned char* kt = k_smem + (size_t)st * TILE_BYTES;
                 unsigned char* vt = v_smem + (size_t)st * TILE_BYTES;
                 if (lane == 0) {
-                    if (g >= 2 && !mbar_wait(&k_empty[st], ph ^ 1)) ok = 0;
+                    if (g >= 2 && !MBAR_WAIT(&k_empty[st], ph ^ 1)) ok = 0;
                     if (ok) {
                         mbar_expect_tx(&k_full[st], n_have * BOXES * PAGE_BYTES);
                         for (int h = 0; h < 2; ++h)
@@ -349,7 +353,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                                 for (int c = 0; c < BOXES; ++c)
                                     tma_load_2d(kt + c * FT_BOX_BYTES + h * PAGE_BYTES, &map_k, c * 64,
                                                 (pg[h] * n_kv + kvh) * FT_PAGE, &k_full[st]);
-                        if (g >= 2 && !mbar_wait(&v_empty[st], ph ^ 1)) ok = 0;
+                        if (g >= 2 && !MBAR_WAIT(&v_empty[st], ph ^ 1)) ok = 0;
                     }
                 }
                 ok = __shfl_sync(FULL, ok, 0);
@@ -373,7 +377,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                                 for (int c = 0; c < BOXES; ++c)
                                     tma_load_2d(vt + c * FT_BOX_BYTES + h * PAGE_BYTES, &map_v, c * 64,
                                                 (pg[h] * n_kv + kvh) * FT_PAGE, tail_bar);
-                        if (!mbar_wait(tail_bar, tail_phase)) ok = 0;
+                        if (!MBAR_WAIT(tail_bar, tail_phase)) ok = 0;
                     }
                     if (n_have > 0) tail_phase ^= 1;
                     ok = __shfl_sync(FULL, ok, 0);
@@ -425,10 +429,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 umma_commit(&k_empty[gt & 1]);
             };
             uint32_t g = 0;
-            bool ok = mbar_wait(&q_full[0], 0);
+            bool ok = MBAR_WAIT(&q_full[0], 0);
             int n_cur = ok ? items[0].n_tiles : 0;
             if (ok && n_cur > 0) {
-                ok = mbar_wait(&k_full[0], 0);
+                ok = MBAR_WAIT(&k_full[0], 0);
                 if (ok) {
                     tc_fence_after();
                     issue_qk(0, 0);
@@ -444,24 +448,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     // the next tile's scores go ahead of this tile's P V: the softmax of the next
                     // tile then runs while the tensor cores work on this one
                     if (i + 1 < n_cur) {
-                        if (!mbar_wait(&k_full[b ^ 1], ((g + 1) >> 1) & 1)) { ok = false; break; }
+                        if (!MBAR_WAIT(&k_full[b ^ 1], ((g + 1) >> 1) & 1)) { ok = false; break; }
                         tc_fence_after();
                         issue_qk(qi, g + 1);
                         if (i + 2 == n_cur) umma_commit(&q_empty[qi]);
                     } else {
                         // the item's last tile: the first tile of the next item, if there is one
-                        if (!mbar_wait(&q_full[qi ^ 1], (uint32_t)((it + 1) >> 1) & 1)) { ok = false; break; }
+                        if (!MBAR_WAIT(&q_full[qi ^ 1], (uint32_t)((it + 1) >> 1) & 1)) { ok = false; break; }
                         n_next = items[qi ^ 1].n_tiles;
                         if (n_next > 0) {
-                            if (!mbar_wait(&k_full[b ^ 1], ((g + 1) >> 1) & 1)) { ok = false; break; }
+                            if (!MBAR_WAIT(&k_full[b ^ 1], ((g + 1) >> 1) & 1)) { ok = false; break; }
                             tc_fence_after();
                             issue_qk(qi ^ 1, g + 1);
                             if (n_next == 1) umma_commit(&q_empty[qi ^ 1]);
                         }
                     }
-                    if (!mbar_wait(&p_full[b], ph) || !mbar_wait(&v_full[b], ph)) { ok = false; break; }
+                    if (!MBAR_WAIT(&p_full[b], ph) || !MBAR_WAIT(&v_full[b], ph)) { ok = false; break; }
                     // the item before the last one had this O buffer: its rows must have been read
-                    if (i == 0 && it >= 2 && !mbar_wait(&o_free[qi], ((uint32_t)(it >> 1) & 1) ^ 1)) { ok = false; break; }
+                    if (i == 0 && it >= 2 && !MBAR_WAIT(&o_free[qi], ((uint32_t)(it >> 1) & 1) ^ 1)) { ok = false; break; }
                     tc_fence_after();
                     const uint64_t vd = v_desc + (b ? SECOND : 0);
                     const uint32_t p_addr = tmem_base + b * S_COLS;
@@ -494,13 +498,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             return ft_write_out<D>(&o_done[e_it & 1], (uint32_t)(e_it >> 1) & 1, &o_free[e_it & 1],
                                    lane_base + O_COL + (uint32_t)(e_it & 1) * D, e_l,
                                    out + (size_t)(e_row0 + warp * 32) * out_stride + (size_t)e_head * D, out_stride,
-                                   e_rows - warp * 32, smem_u32(stage_smem) + warp * 4096);
+                                   e_rows - warp * 32, smem_u32(stage_smem) + warp * 4096, spin_limit);
         };
         uint32_t g = 0;
         // every wait's outcome is agreed on by the whole warp: the tensor-memory accesses are warp-wide
         for (int it = 0; ok; ++it) {
             const int qi = it & 1;
-            if (!__all_sync(FULL, mbar_wait(&q_full[qi], (uint32_t)(it >> 1) & 1))) { ok = false; timed_out = true; break; }
+            if (!__all_sync(FULL, MBAR_WAIT(&q_full[qi], (uint32_t)(it >> 1) & 1))) { ok = false; timed_out = true; break; }
             const int n_tiles = items[qi].n_tiles, j_beg = items[qi].j_beg, p0 = items[qi].p0, seq_hi = items[qi].seq_hi;
             const int row0 = items[qi].row0, rows = items[qi].rows, head = items[qi].head;
             __syncwarp();
@@ -514,7 +518,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 if (__any_sync(FULL, *s_flag != 0)) { ok = false; break; }
                 const int j = j_beg + i;
                 const uint32_t b = g & 1, ph = (g >> 1) & 1;
-                if (!__all_sync(FULL, mbar_wait(&s_full[b], ph))) { ok = false; timed_out = true; break; }
+                if (!__all_sync(FULL, MBAR_WAIT(&s_full[b], ph))) { ok = false; timed_out = true; break; }
                 tc_fence_after();
                 float s[FT_KEYS];
                 const uint32_t s_addr = lane_base + b * S_COLS;
@@ -543,7 +547,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 if (__any_sync(FULL, raise && i > 0)) {
                     const float m_new = raise ? mx : m_used;
                     const float f = (raise && m_used > -INFINITY) ? ft_exp2((m_used - m_new) * scale_log2) : 1.0f;
-                    if (!__all_sync(FULL, mbar_wait(o_tile, (g - 1) & 1))) {     // O holds the item's tiles 0 .. i-1
+                    if (!__all_sync(FULL, MBAR_WAIT(o_tile, (g - 1) & 1))) {     // O holds the item's tiles 0 .. i-1
                         ok = false;
                         timed_out = true;
                         break;
@@ -601,11 +605,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (*s_flag && warp == 4 && lane == 0) {
         // a wait ran out: give outstanding TMA writes a bounded time to land
         for (int s = 0; s < 2; ++s) {
-            mbar_wait(&q_full[s], 0), mbar_wait(&q_full[s], 1);
-            mbar_wait(&k_full[s], 0), mbar_wait(&k_full[s], 1);
-            mbar_wait(&v_full[s], 0), mbar_wait(&v_full[s], 1);
+            MBAR_WAIT(&q_full[s], 0), MBAR_WAIT(&q_full[s], 1);
+            MBAR_WAIT(&k_full[s], 0), MBAR_WAIT(&k_full[s], 1);
+            MBAR_WAIT(&v_full[s], 0), MBAR_WAIT(&v_full[s], 1);
         }
-        mbar_wait(tail_bar, 0), mbar_wait(tail_bar, 1);
+        MBAR_WAIT(tail_bar, 0), MBAR_WAIT(tail_bar, 1);
     }
     __syncthreads();
     if (warp == 5) {
@@ -628,7 +632,7 @@ static int launch_prefill_tc(const void* qkv, long q_stride, void* out, long out
                              const void* v_pages, long n_pages, const int* block_table, int table_stride,
                              const int* cu_seqlens, const int* seq_slot, const int* seq_start, int n_seqs, long n_tokens,
                              int max_seq_tokens, int n_q, int n_kv, int window, float scale, int* status,
-                             cudaStream_t stream) {
+                             cudaStream_t stream, TcWaits waits) {
     CUtensorMap mq, mk, mv;
     int rc = bfi_tensor_map_bf16(qkv, n_tokens, (long)n_q * D, q_stride, FT_ROWS, &mq);
     if (rc) return rc;
@@ -642,14 +646,11 @@ static int launch_prefill_tc(const void* qkv, long q_stride, void* out, long out
     const size_t smem = tiles > 120 * 1024 ? tiles : 120 * 1024;
     auto kernel = attention_prefill_tc_kernel<D>;
     static bool configured = false;
-    static int n_sm = 148;
+    const int n_sm = bfi_sm_count();
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return bfi_fail("attention_prefill_tcgen05: cannot reserve %zu bytes of shared memory: %s", smem,
                                               cudaGetErrorString(e));
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
         configured = true;
     }
     const unsigned lbo = FT_BOX_BYTES;      // leading byte offset: between the two 64-wide halves of the head
@@ -659,7 +660,7 @@ static int launch_prefill_tc(const void* qkv, long q_stride, void* out, long out
     dim3 grid((unsigned)(items < n_sm ? items : n_sm));      // one block per SM, each drawing items until none is left
     bfi_launch(kernel, grid, dim3(FT_THREADS), smem, stream, mq, mk, mv, (bf16*)out, out_stride, block_table, table_stride,
                cu_seqlens, seq_slot, seq_start, n_seqs, max_tiles, n_q, n_kv, window, scale * 1.4426950408889634f,
-               (uint32_t)lbo, (uint32_t)sbo, status, status + 1);
+               (uint32_t)lbo, (uint32_t)sbo, status, status + 1, waits);
     return bfi_check_launch("attention_prefill_tcgen05");
 }
 
@@ -670,12 +671,11 @@ static int launch_prefill_tc(const void* qkv, long q_stride, void* out, long out
 // zero before the first call: [0] gets BFI_STATUS_TIMEOUT when a wait ran out, [1] and [2] are
 // the counters of tickets drawn and blocks finished, which every launch leaves at zero again; two
 // launches that may run at the same time need status words of their own.
-extern "C" int bfi_attention_prefill_tcgen05_bf16(const void* qkv, long q_stride, void* out, long out_stride,
-                                                  const void* k_pages, const void* v_pages, long n_pages,
-                                                  const int* block_table, int table_stride, const int* cu_seqlens,
-                                                  const int* seq_slot, const int* seq_start, int n_seqs, long n_tokens,
-                                                  int max_seq_tokens, int n_q, int n_kv, int d, int window, float scale,
-                                                  int* status, cudaStream_t stream) {
+static int attention_prefill_tc_launch(const void* qkv, long q_stride, void* out, long out_stride, const void* k_pages,
+                                       const void* v_pages, long n_pages, const int* block_table, int table_stride,
+                                       const int* cu_seqlens, const int* seq_slot, const int* seq_start, int n_seqs,
+                                       long n_tokens, int max_seq_tokens, int n_q, int n_kv, int d, int window, float scale,
+                                       int* status, cudaStream_t stream, TcWaits waits) {
     BFI_REQUIRE(n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_prefill_tcgen05: %d query heads do not divide into %d kv heads",
                 n_q, n_kv);
     BFI_REQUIRE(window >= 0 && status != nullptr, "attention_prefill_tcgen05: bad window or no status word");
@@ -688,8 +688,39 @@ extern "C" int bfi_attention_prefill_tcgen05_bf16(const void* qkv, long q_stride
     if (d == 64)
         return launch_prefill_tc<64>(qkv, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, table_stride,
                                      cu_seqlens, seq_slot, seq_start, n_seqs, n_tokens, max_seq_tokens, n_q, n_kv, window,
-                                     scale, status, stream);
+                                     scale, status, stream, waits);
     return launch_prefill_tc<128>(qkv, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, table_stride,
                                   cu_seqlens, seq_slot, seq_start, n_seqs, n_tokens, max_seq_tokens, n_q, n_kv, window, scale,
-                                  status, stream);
+                                  status, stream, waits);
+}
+
+extern "C" int bfi_attention_prefill_tcgen05_bf16(const void* qkv, long q_stride, void* out, long out_stride,
+                                                  const void* k_pages, const void* v_pages, long n_pages,
+                                                  const int* block_table, int table_stride, const int* cu_seqlens,
+                                                  const int* seq_slot, const int* seq_start, int n_seqs, long n_tokens,
+                                                  int max_seq_tokens, int n_q, int n_kv, int d, int window, float scale,
+                                                  int* status, cudaStream_t stream) {
+    return attention_prefill_tc_launch(qkv, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, table_stride,
+                                       cu_seqlens, seq_slot, seq_start, n_seqs, n_tokens, max_seq_tokens, n_q, n_kv, d, window,
+                                       scale, status, stream, tc_waits_default());
+}
+
+// For the tests of the time-out path: the same launch, but every bounded wait gives up after
+// `spin_limit` polls (at most 65536 here) and, with hold_producer != 0, the producer warp draws no
+// item and issues no copy, so that the first wait of every other role runs out by construction.
+// The launch records BFI_STATUS_TIMEOUT in status[0], leaves the ticket counters at zero, frees its
+// tensor memory and returns; `out` is not written.  No fault, no trap, nothing unbounded.
+extern "C" int bfi_attention_prefill_tcgen05_bf16_wait_probe(const void* qkv, long q_stride, void* out, long out_stride,
+                                                             const void* k_pages, const void* v_pages, long n_pages,
+                                                             const int* block_table, int table_stride,
+                                                             const int* cu_seqlens, const int* seq_slot,
+                                                             const int* seq_start, int n_seqs, long n_tokens,
+                                                             int max_seq_tokens, int n_q, int n_kv, int d, int window,
+                                                             float scale, int* status, unsigned spin_limit,
+                                                             int hold_producer, cudaStream_t stream) {
+    BFI_REQUIRE(spin_limit >= 1 && spin_limit <= 65536, "attention_prefill_tcgen05 wait probe: spin limit %u outside 1..65536",
+                spin_limit);
+    return attention_prefill_tc_launch(qkv, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, table_stride,
+                                       cu_seqlens, seq_slot, seq_start, n_seqs, n_tokens, max_seq_tokens, n_q, n_kv, d, window,
+                                       scale, status, stream, TcWaits{spin_limit, hold_producer ? 1 : 0});
 }

@@ -28,6 +28,7 @@ typedef __nv_bfloat16 bf16;
 extern "C" const char* bfi_last_error();
 int bfi_fail(const char* fmt, ...);
 int bfi_check_launch(const char* what);
+int bfi_sm_count();
 
 // Programmatic dependent launch.  When enabled, every kernel is launched with the attribute that
 // lets it start while its predecessor in the stream drains.  A kernel may touch nothing but

@@ -202,7 +202,7 @@ extern "C" int bfi_silu_mul(const void* gu, long in_stride, void* out, long out_
     if (n_rows == 0) return 0;
     const long total = (long)n_rows * inter;
     const int threads = 256;
-    const int blocks = (int)((total + threads - 1) / threads < 148L * 16 ? (total + threads - 1) / threads : 148L * 16);
+    const int blocks = (int)((total + threads - 1) / threads < bfi_sm_count() * 16L ? (total + threads - 1) / threads : bfi_sm_count() * 16L);
     if (dtype == BFI_F32)
         bfi_launch(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)gu, in_stride, (float*)out, out_stride,
                                                                n_rows, inter, interleaved);
@@ -530,7 +530,7 @@ extern "C" int bfi_residual_add(float* x, const void* y, int y_dtype, long n, cu
     if (n <= 0) return 0;
     const int threads = 256;
     const long want = (n + threads - 1) / threads;
-    const int blocks = (int)(want < 148L * 16 ? want : 148L * 16);
+    const int blocks = (int)(want < bfi_sm_count() * 16L ? want : bfi_sm_count() * 16L);
     if (y_dtype == BFI_F32)
         bfi_launch(residual_add_kernel<float>, dim3(blocks), dim3(threads), 0, stream, x, (const float*)y, n);
     else

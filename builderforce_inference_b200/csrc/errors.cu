@@ -31,5 +31,24 @@ extern "C" int bfi_set_pdl(int on) {
     return 0;
 }
 
+// Multiprocessors of the current device, asked of the driver once per device: launchers size
+// their grids and work splits by it instead of by a constant.
+int bfi_sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            n = 148;      // no device to ask (a build check without a GPU): a B200's count
+        }
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+extern "C" int bfi_device_sm_count() { return bfi_sm_count(); }
+
 // Identifies the build: the architecture the device code was compiled for.
 extern "C" const char* bfi_build_arch() { return "sm_100a"; }

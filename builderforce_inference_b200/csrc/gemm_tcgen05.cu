@@ -55,8 +55,9 @@ template <int BT>
 __global__ void __launch_bounds__(TC_THREADS, TcConfig<BT>::BLOCKS_PER_SM)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                     void* __restrict__ C, int c_dtype, long ldc, int M, int N, int K, int kblocks_per_split,
-                    int epilogue, int* __restrict__ status) {
+                    int epilogue, int* __restrict__ status, TcWaits waits) {
     using Cfg = TcConfig<BT>;
+    const uint32_t spin_limit = waits.spin_limit;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES);
@@ -99,7 +100,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (lane == 0) {
             // W does not depend on the kernel before this one: the ring fills with W tiles before the
             // wait for that kernel (programmatic dependent launch), the A tiles follow after it
-            const int early = n_kb < Cfg::STAGES ? n_kb : Cfg::STAGES;
+            const int early = waits.hold_producer ? 0 : (n_kb < Cfg::STAGES ? n_kb : Cfg::STAGES);
             pdl_trigger();
             for (int i = 0; i < early; ++i) {
                 mbar_expect_tx(&full[i], Cfg::STAGE_BYTES);
@@ -108,10 +109,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             pdl_wait();
             for (int i = 0; i < early; ++i)
                 tma_load_2d(smem + (size_t)i * Cfg::STAGE_BYTES + TC_ROWS * TC_BK * 2, &map_a, (kb_beg + i) * TC_BK, m0, &full[i]);
-            for (int i = early; i < n_kb; ++i) {
+            for (int i = early; i < n_kb && !waits.hold_producer; ++i) {
                 const int s = i % Cfg::STAGES;
                 const uint32_t phase = (i / Cfg::STAGES) & 1;
-                if (!mbar_wait(&empty[s], phase ^ 1)) {
+                if (!MBAR_WAIT(&empty[s], phase ^ 1)) {
                     atomicOr(status, BFI_STATUS_TIMEOUT);
                     s_flag[0] = 1;
                     break;
@@ -134,7 +135,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             for (int i = 0; i < n_kb && ok; ++i) {
                 const int s = i % Cfg::STAGES;
                 const uint32_t phase = (i / Cfg::STAGES) & 1;
-                if (!mbar_wait(&full[s], phase)) {
+                if (!MBAR_WAIT(&full[s], phase)) {
                     atomicOr(status, BFI_STATUS_TIMEOUT);
                     s_flag[0] = 1;
                     ok = false;
@@ -171,7 +172,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (3 < per_rank && j0 + 3 < BT && m0 + j0 + 3 < M) c_pre3 = c_in[(size_t)(m0 + j0 + 3) * ldc + n];
         }
         if (n_kb > 0) {
-            ok = mbar_wait(tmem_full, 0);
+            ok = MBAR_WAIT(tmem_full, 0);
             if (!ok && lane == 0) {
                 atomicOr(status, BFI_STATUS_TIMEOUT);
                 s_flag[0] = 1;
@@ -280,7 +281,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         // a wait ran out: let outstanding TMA writes land (bounded) before the block's memory is reused
         for (int s = 0; s < Cfg::STAGES && s < n_kb; ++s) {
             const int last = ((n_kb - 1 - s) / Cfg::STAGES) * Cfg::STAGES + s;   // last k block that used stage s
-            mbar_wait(&full[s], (uint32_t)((last / Cfg::STAGES) & 1));
+            MBAR_WAIT(&full[s], (uint32_t)((last / Cfg::STAGES) & 1));
         }
     }
     __syncthreads();
@@ -311,7 +312,8 @@ template <int HALVES>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                             void* __restrict__ C, int c_dtype, long ldc, int M, int N, int K, int tiles_m, int tiles_n,
-                            int tile_n, int n_stages, int epilogue, int vec_ok, int* __restrict__ status) {
+                            int tile_n, int n_stages, int epilogue, int vec_ok, int* __restrict__ status, TcWaits waits) {
+    const uint32_t spin_limit = waits.spin_limit;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)TP_RING_BYTES);
@@ -363,7 +365,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         if (lane == 0) {
             int it = 0;                                            // k blocks issued so far, over all tiles
             bool first = true;
-            for (int tile = blockIdx.x; tile < n_tiles && !s_flag[0]; tile += gridDim.x) {
+            for (int tile = blockIdx.x; tile < n_tiles && !s_flag[0] && !waits.hold_producer; tile += gridDim.x) {
                 int tm, tn;
                 tile_coords(tile, tm, tn);
                 int i0 = 0;
@@ -385,7 +387,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                 for (int i = i0; i < n_kb; ++i, ++it) {
                     const int s = it % n_stages;
                     const uint32_t phase = (it / n_stages) & 1;
-                    if (it >= n_stages && !mbar_wait(&empty[s], phase ^ 1)) {
+                    if (it >= n_stages && !MBAR_WAIT(&empty[s], phase ^ 1)) {
                         atomicOr(status, BFI_STATUS_TIMEOUT);
                         s_flag[0] = 1;
                         break;
@@ -410,12 +412,12 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                 // epilogue has drained it.
                 const int acc = local & 1;
                 bool ok = true;
-                if (HALVES == 1 && local >= 2 && !mbar_wait(&tmem_empty[acc], (((uint32_t)(local >> 1)) & 1) ^ 1)) ok = false;
+                if (HALVES == 1 && local >= 2 && !MBAR_WAIT(&tmem_empty[acc], (((uint32_t)(local >> 1)) & 1) ^ 1)) ok = false;
                 tc_fence_after();
                 for (int i = 0; ok && i < n_kb; ++i, ++it) {
                     const int s = it % n_stages;
                     const uint32_t phase = (it / n_stages) & 1;
-                    if (!mbar_wait(&full[s], phase)) {
+                    if (!MBAR_WAIT(&full[s], phase)) {
                         ok = false;
                         break;
                     }
@@ -425,7 +427,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 #pragma unroll
                     for (int h = 0; h < HALVES; ++h) {
                         if (HALVES == 2 && i == 0 && local >= 1) {
-                            if (!mbar_wait(&tmem_empty[h], (uint32_t)((local - 1) & 1))) {
+                            if (!MBAR_WAIT(&tmem_empty[h], (uint32_t)((local - 1) & 1))) {
                                 ok = false;
                                 break;
                             }
@@ -458,7 +460,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             tile_coords(tile, tm, tn);
             const int full_idx = HALVES == 1 ? (local & 1) : 0;
             const uint32_t full_parity = HALVES == 1 ? (uint32_t)((local >> 1) & 1) : (uint32_t)(local & 1);
-            if (!mbar_wait(&tmem_full[full_idx], full_parity)) {
+            if (!MBAR_WAIT(&tmem_full[full_idx], full_parity)) {
                 if (lane == 0) {
                     atomicOr(status, BFI_STATUS_TIMEOUT);
                     s_flag[0] = 1;
@@ -553,7 +555,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     __syncthreads();
     if (s_flag[0] && warp == 0 && lane == 0) {
         // a wait ran out: give outstanding TMA writes a bounded time to land
-        for (int s = 0; s < n_stages; ++s) mbar_wait(&full[s], 0), mbar_wait(&full[s], 1);
+        for (int s = 0; s < n_stages; ++s) MBAR_WAIT(&full[s], 0), MBAR_WAIT(&full[s], 1);
     }
     __syncthreads();
     if (warp == 1) {
@@ -632,13 +634,28 @@ struct TcPlan {
     int bt, tiles_n, tiles_m, ksplit, kblocks_per_split;
 };
 
-static int g_tc_tune_ksplit = 0;
-extern "C" int bfi_gemm_tcgen05_tune(int ksplit) {
-    g_tc_tune_ksplit = ksplit;
+// Overrides of the planners' choices, for tests and experiments.  An override holds for ONE call of
+// bfi_gemm_tcgen05_bf16 (the next one, which takes it and clears it, whether or not it launches), so
+// nothing a test sets can outlive that test.  0 keeps the built-in choice.
+struct TcTune {
+    int ksplit;      // few-row kernel: splits of K
+    int tile_n;      // many-row kernel: features per tile
+    int halves;      // many-row kernel: one or two halves of 128 tokens
+};
+static TcTune g_tc_tune = {0, 0, 0};
+static TcTune take_tc_tune() {
+    const TcTune t = g_tc_tune;
+    g_tc_tune = TcTune{0, 0, 0};
+    return t;
+}
+extern "C" int bfi_gemm_tcgen05_tune_next(int ksplit, int tile_n, int halves) {
+    g_tc_tune.ksplit = ksplit > 0 ? ksplit : 0;
+    g_tc_tune.tile_n = (tile_n >= 16 && tile_n <= TP_FEATS && tile_n % 16 == 0) ? tile_n : 0;
+    g_tc_tune.halves = (halves == 1 || halves == 2) ? halves : 0;
     return 0;
 }
 
-static TcPlan plan_tc(int M, int N, int K) {
+static TcPlan plan_tc(int M, int N, int K, int g_tc_tune_ksplit) {
     const bool allow_split = true;
     TcPlan p;
     p.bt = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)));
@@ -647,7 +664,7 @@ static TcPlan plan_tc(int M, int N, int K) {
     const int kblocks = (K + TC_BK - 1) / TC_BK;
     p.ksplit = 1;
     const long tiles = (long)p.tiles_n * p.tiles_m;
-    const long slots = p.bt <= 64 ? 296 : 148;          // blocks resident at once
+    const long slots = (p.bt <= 64 ? 2L : 1L) * bfi_sm_count();     // blocks resident at once
     if (allow_split && tiles * 2 <= slots) {
         // few tiles: split K so that the grid fills the resident slots in one wave, with at least
         // 8 k blocks per split (shorter runs cost more in fill and reduction than they gain)
@@ -664,7 +681,7 @@ static TcPlan plan_tc(int M, int N, int K) {
 
 template <int BT>
 static int launch_tc(const TcPlan& p, const CUtensorMap& mw, const CUtensorMap& ma, void* C, int c_dtype, long ldc,
-                     int M, int N, int K, int epilogue, int* status, cudaStream_t stream) {
+                     int M, int N, int K, int epilogue, int* status, cudaStream_t stream, TcWaits waits) {
     using Cfg = TcConfig<BT>;
     auto kernel = gemm_tcgen05_kernel<BT>;
     static bool configured = false;
@@ -695,7 +712,7 @@ static int launch_tc(const TcPlan& p, const CUtensorMap& mw, const CUtensorMap& 
     }
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mw, ma, C, c_dtype, ldc, M, N, K, p.kblocks_per_split, epilogue, status);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, mw, ma, C, c_dtype, ldc, M, N, K, p.kblocks_per_split, epilogue, status, waits);
     if (e != cudaSuccess) {
         cudaGetLastError();
         return bfi_fail("gemm_tcgen05: launch failed: %s", cudaGetErrorString(e));
@@ -703,19 +720,11 @@ static int launch_tc(const TcPlan& p, const CUtensorMap& mw, const CUtensorMap& 
     return bfi_check_launch("gemm_tcgen05");
 }
 
-// tests and experiments: force the tile of the persistent kernel (0 = choose): features per tile,
-// and one or two halves of 128 tokens
-static int g_tp_tune_tile_n = 0, g_tp_tune_halves = 0;
-extern "C" int bfi_gemm_tcgen05_tune_tile(int tile_n, int halves) {
-    g_tp_tune_tile_n = (tile_n >= 16 && tile_n <= TP_FEATS && tile_n % 16 == 0) ? tile_n : 0;
-    g_tp_tune_halves = (halves == 1 || halves == 2) ? halves : 0;
-    return 0;
-}
-
 static int launch_tc_prefill(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype, long ldc, int M,
-                             int N, int K, int epilogue, int* status, cudaStream_t stream) {
+                             int N, int K, int epilogue, int* status, cudaStream_t stream, TcWaits waits, TcTune tune) {
+    const int g_tp_tune_tile_n = tune.tile_n, g_tp_tune_halves = tune.halves;
     static bool configured = false;
-    static int n_sm = 148;
+    const int n_sm = bfi_sm_count();
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_prefill_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)TP_SMEM);
@@ -723,9 +732,6 @@ static int launch_tc_prefill(const void* A, long lda, const void* W, long ldw, v
             e = cudaFuncSetAttribute(gemm_tcgen05_prefill_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TP_SMEM);
         if (e != cudaSuccess)
             return bfi_fail("gemm_tcgen05: cannot reserve %zu bytes of shared memory: %s", (size_t)TP_SMEM, cudaGetErrorString(e));
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
         configured = true;
     }
     // The tile (one or two halves of 128 tokens x tile_n features) that takes the least time by an
@@ -772,28 +778,27 @@ static int launch_tc_prefill(const void* A, long lda, const void* W, long ldw, v
     const int vec_ok = ((ldc * elem) % 16 == 0 && ((uintptr_t)C & 15) == 0) ? 1 : 0;
     if (halves == 2)
         bfi_launch(gemm_tcgen05_prefill_kernel<2>, dim3(grid), dim3(TC_THREADS), TP_SMEM, stream, ma, mw, C, c_dtype, ldc, M, N,
-                   K, tiles_m, tiles_n, tile_n, n_stages, epilogue, vec_ok, status);
+                   K, tiles_m, tiles_n, tile_n, n_stages, epilogue, vec_ok, status, waits);
     else
         bfi_launch(gemm_tcgen05_prefill_kernel<1>, dim3(grid), dim3(TC_THREADS), TP_SMEM, stream, ma, mw, C, c_dtype, ldc, M, N,
-                   K, tiles_m, tiles_n, tile_n, n_stages, epilogue, vec_ok, status);
+                   K, tiles_m, tiles_n, tile_n, n_stages, epilogue, vec_ok, status, waits);
     return bfi_check_launch("gemm_tcgen05_prefill");
 }
 
-// Returns 0 on success, 1 on error, 2 when the shape is not taken (nothing launched).
-// `status` receives BFI_STATUS_TIMEOUT (8) if a bounded wait inside the kernel ran out.
-extern "C" int bfi_gemm_tcgen05_bf16(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype, long ldc,
-                                     int M, int N, int K, int epilogue, int* status, cudaStream_t stream) {
+static int gemm_tcgen05_launch(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype, long ldc, int M,
+                               int N, int K, int epilogue, int* status, cudaStream_t stream, TcWaits waits) {
     BFI_REQUIRE(dtype_ok(c_dtype), "gemm_tcgen05: unknown output dtype code %d", c_dtype);
     BFI_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
     BFI_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_tcgen05: unknown epilogue %d", epilogue);
     BFI_REQUIRE(status != nullptr, "gemm_tcgen05: a status word is required");
     if (epilogue == EPI_ACCUMULATE) BFI_REQUIRE(c_dtype == BFI_F32, "gemm_tcgen05: accumulation needs a float32 output");
     if (epilogue == EPI_SWIGLU) BFI_REQUIRE(N % 2 == 0, "gemm_tcgen05: the gated epilogue needs an even N, got %d", N);
+    const TcTune tune = take_tc_tune();
     if (M == 0) return 0;
     // TMA: 16-byte aligned bases and row strides
     if (K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return 2;
-    if (M >= 128) return launch_tc_prefill(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, status, stream);
-    TcPlan p = plan_tc(M, N, K);
+    if (M >= 128) return launch_tc_prefill(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, status, stream, waits, tune);
+    TcPlan p = plan_tc(M, N, K, tune.ksplit);
     if (p.tiles_m > 65535) return 2;
     CUtensorMap mw, ma;
     int rc = bfi_tensor_map_bf16(W, N, K, ldw, TC_ROWS, &mw);
@@ -801,10 +806,31 @@ extern "C" int bfi_gemm_tcgen05_bf16(const void* A, long lda, const void* W, lon
     rc = bfi_tensor_map_bf16(A, M, K, lda, p.bt, &ma);
     if (rc) return rc;
     switch (p.bt) {
-        case 16: return launch_tc<16>(p, mw, ma, C, c_dtype, ldc, M, N, K, epilogue, status, stream);
-        case 32: return launch_tc<32>(p, mw, ma, C, c_dtype, ldc, M, N, K, epilogue, status, stream);
-        case 64: return launch_tc<64>(p, mw, ma, C, c_dtype, ldc, M, N, K, epilogue, status, stream);
-        case 128: return launch_tc<128>(p, mw, ma, C, c_dtype, ldc, M, N, K, epilogue, status, stream);
-        default: return launch_tc<256>(p, mw, ma, C, c_dtype, ldc, M, N, K, epilogue, status, stream);
+        case 16: return launch_tc<16>(p, mw, ma, C, c_dtype, ldc, M, N, K, epilogue, status, stream, waits);
+        case 32: return launch_tc<32>(p, mw, ma, C, c_dtype, ldc, M, N, K, epilogue, status, stream, waits);
+        case 64: return launch_tc<64>(p, mw, ma, C, c_dtype, ldc, M, N, K, epilogue, status, stream, waits);
+        case 128: return launch_tc<128>(p, mw, ma, C, c_dtype, ldc, M, N, K, epilogue, status, stream, waits);
+        default: return launch_tc<256>(p, mw, ma, C, c_dtype, ldc, M, N, K, epilogue, status, stream, waits);
     }
+}
+
+// Returns 0 on success, 1 on error, 2 when the shape is not taken (nothing launched).
+// `status` receives BFI_STATUS_TIMEOUT (8) if a bounded wait inside the kernel ran out.
+extern "C" int bfi_gemm_tcgen05_bf16(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype, long ldc,
+                                     int M, int N, int K, int epilogue, int* status, cudaStream_t stream) {
+    return gemm_tcgen05_launch(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, status, stream, tc_waits_default());
+}
+
+// For the tests of the time-out path: the same launch, but every bounded wait gives up after
+// `spin_limit` polls (at most 65536 here, so the launch ends within milliseconds) and, with
+// hold_producer != 0, the thread that issues the TMA copies issues none.  The consumers' waits then
+// run out by construction: the launch records BFI_STATUS_TIMEOUT in `status`, gives its copies (there
+// are none) a bounded time to land, frees its tensor memory and returns; C holds nothing of use.
+// No fault, no trap and no unbounded wait is involved.
+extern "C" int bfi_gemm_tcgen05_bf16_wait_probe(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype,
+                                                long ldc, int M, int N, int K, int epilogue, int* status,
+                                                unsigned spin_limit, int hold_producer, cudaStream_t stream) {
+    BFI_REQUIRE(spin_limit >= 1 && spin_limit <= 65536, "gemm_tcgen05 wait probe: spin limit %u outside 1..65536", spin_limit);
+    return gemm_tcgen05_launch(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, status, stream,
+                               TcWaits{spin_limit, hold_producer ? 1 : 0});
 }

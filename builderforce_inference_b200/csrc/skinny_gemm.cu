@@ -234,16 +234,27 @@ __global__ void skinny_gemm_kernel(const bf16* __restrict__ A, long lda, const b
     }
 }
 
-// Tuning overrides for experiments: 0 keeps the built-in choice.
+// Overrides of the plan for tests and experiments: 0 keeps the built-in choice.  An override holds
+// for ONE call of a product entry point (the next one, which clears it when it returns, whether or
+// not it launched), so nothing a test sets can outlive that test; bfi_skinny_gemm_scratch, which
+// only asks for a plan's sizes, sees the pending override and leaves it standing.
 static int g_tune_warps = 0;
 static int g_tune_prefetch = 0;
 static int g_tune_ksplit = 0;
-extern "C" int bfi_skinny_tune(int warps, int prefetch, int ksplit) {
+extern "C" int bfi_skinny_tune_next(int warps, int prefetch, int ksplit) {
     g_tune_warps = warps;
     g_tune_prefetch = prefetch;
     g_tune_ksplit = ksplit;
     return 0;
 }
+struct SkinnyTuneScope {       // clears the override when the entry point that owns it returns
+    bool owner;
+    explicit SkinnyTuneScope(bool o) : owner(o) {}
+    ~SkinnyTuneScope() {
+        if (owner) g_tune_warps = g_tune_prefetch = g_tune_ksplit = 0;
+    }
+};
+static int g_skinny_entry_depth = 0;
 
 // The plan of a launch: warps per block, split of K between blocks, scratch it needs.
 struct SkinnyPlan {
@@ -257,12 +268,13 @@ static SkinnyPlan plan_skinny(int rows_per_tile, int m_pad, int N, int K, bool a
     SkinnyPlan p;
     p.tiles = (N + rows_per_tile - 1) / rows_per_tile;
     // many tiles: small blocks, several per SM; few tiles: wider blocks and K split between blocks
-    p.warps = p.tiles >= 600 ? 4 : 8;
+    const int sms = bfi_sm_count();
+    p.warps = p.tiles >= 4 * sms ? 4 : 8;
     if (g_tune_warps > 0) p.warps = g_tune_warps;
     while (p.warps > 1 && K / p.warps < 64) p.warps >>= 1;
     p.ksplit = 1;
-    if (allow_split && p.tiles < 300) {
-        p.ksplit = (296 + p.tiles - 1) / p.tiles;       // about two blocks per SM
+    if (allow_split && p.tiles < 2 * sms) {
+        p.ksplit = (2 * sms + p.tiles - 1) / p.tiles;   // about two blocks per SM
         while (p.ksplit > 1 && K / (p.ksplit * p.warps) < 128) --p.ksplit;
     }
     if (g_tune_ksplit > 0 && allow_split) p.ksplit = g_tune_ksplit;
@@ -307,11 +319,11 @@ extern "C" int bfi_skinny_gemm_scratch(int M, int N, int K, long* sizes) {
     return 0;
 }
 
-// Returns 0 on success, 1 on error, and 2 when the shape is not taken (nothing launched; the
-// caller uses the general kernel).
-extern "C" int bfi_skinny_gemm_bf16(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype, long ldc,
-                                    int M, int N, int K, int epilogue, float* scratch, long scratch_floats,
-                                    int* counters, int n_counters, cudaStream_t stream) {
+// The checks every entry point makes before it puts anything on the stream: 0 when the call may
+// go ahead (or has nothing to do, M == 0), 1 on an error (the text is left for bfi_last_error), 2
+// when the shape is not one the kernel takes.
+static int skinny_check_args(const void* A, long lda, const void* W, long ldw, int c_dtype, int M, int N, int K,
+                             int epilogue) {
     BFI_REQUIRE(dtype_ok(c_dtype), "skinny_gemm: unknown output dtype code %d", c_dtype);
     BFI_REQUIRE(M >= 0 && N > 0 && K > 0, "skinny_gemm: bad sizes M=%d N=%d K=%d", M, N, K);
     BFI_REQUIRE(epilogue >= 0 && epilogue <= 2, "skinny_gemm: unknown epilogue %d", epilogue);
@@ -320,6 +332,17 @@ extern "C" int bfi_skinny_gemm_bf16(const void* A, long lda, const void* W, long
     if (M == 0) return 0;
     // 16-byte loads: K a multiple of 8, rows and bases 16-byte aligned
     if (M > 64 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return 2;
+    return 0;
+}
+
+// Returns 0 on success, 1 on error, and 2 when the shape is not taken (nothing launched; the
+// caller uses the general kernel).
+extern "C" int bfi_skinny_gemm_bf16(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype, long ldc,
+                                    int M, int N, int K, int epilogue, float* scratch, long scratch_floats,
+                                    int* counters, int n_counters, cudaStream_t stream) {
+    SkinnyTuneScope scope(g_skinny_entry_depth == 0);
+    const int verdict = skinny_check_args(A, lda, W, ldw, c_dtype, M, N, K, epilogue);
+    if (verdict != 0 || M == 0) return verdict;
     const bf16* a = (const bf16*)A;
     const bf16* w = (const bf16*)W;
     const bool wide = skinny_wide(M, N);   // many rows: two m-tiles per block halve the activation traffic
@@ -367,9 +390,14 @@ static int static_scratch_address(float** out) {
 
 extern "C" int bfi_skinny_gemm_bf16_static(const void* A, long lda, const void* W, long ldw, void* C, int c_dtype,
                                            long ldc, int M, int N, int K, int epilogue, cudaStream_t stream) {
-    BFI_REQUIRE(M >= 0 && N > 0 && K > 0, "skinny_gemm_static: bad sizes M=%d N=%d K=%d", M, N, K);
-    if (M == 0) return 0;
-    if (M > 64) return 2;
+    SkinnyTuneScope scope(true);
+    struct Depth {
+        Depth() { ++g_skinny_entry_depth; }
+        ~Depth() { --g_skinny_entry_depth; }
+    } depth;                                   // the inner call must not clear the override before it planned
+    // every refusal comes before the first thing this call puts on the stream
+    const int verdict = skinny_check_args(A, lda, W, ldw, c_dtype, M, N, K, epilogue);
+    if (verdict != 0 || M == 0) return verdict;
     long need[2] = {0, 0};
     bfi_skinny_gemm_scratch(M, N, K, need);
     const long room = (long)BFI_STATIC_SCRATCH_FLOATS - BFI_STATIC_COUNTER_SLOTS;

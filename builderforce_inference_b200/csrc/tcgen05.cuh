@@ -31,12 +31,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i)
+// Bounded wait: false when `limit` polls ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit) {
+    for (uint32_t i = 0; i < limit; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
+// How a launch's bounded waits behave.  Every ordinary launch passes {TC_SPIN_LIMIT, 0}.  The
+// probe entry points, which exist for the tests of the time-out path, pass a small limit and
+// hold_producer = 1: the producer thread then issues no copy at all, so the consumers' waits run
+// out by construction after `spin_limit` polls each (no fault, no trap, nothing unbounded), and
+// the launch must record BFI_STATUS_TIMEOUT, drain, free its tensor memory and return.
+struct TcWaits {
+    uint32_t spin_limit;
+    int hold_producer;
+};
+static inline TcWaits tc_waits_default() { return TcWaits{TC_SPIN_LIMIT, 0}; }
+// inside a kernel that has `spin_limit` in scope
+#define MBAR_WAIT(bar, parity) mbar_wait((bar), (parity), spin_limit)
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"

@@ -11,7 +11,21 @@ from .library import KernelError, library
 from .ops import _ptr, _rows_2d, _stream, dtype_code
 
 SKINNY_MAX_ROWS = 64
-SM_COUNT = 148
+
+_sm_count = {}
+
+
+def sm_count(device=None) -> int:
+    """Multiprocessors of ``device`` (the current one by default), asked of the driver once."""
+    index = torch.cuda.current_device() if device is None else torch.device(device).index
+    if index is None:
+        index = torch.cuda.current_device()
+    n = _sm_count.get(index)
+    if n is None:
+        with torch.cuda.device(index):
+            n = int(library("fast").lib.bfi_device_sm_count())
+        _sm_count[index] = n
+    return n
 
 
 class _SplitScratch:
@@ -114,6 +128,18 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: 
         _ptr(tc_status(a.device)), _stream())
 
 
+def gemm_tcgen05_wait_probe(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, spin_limit: int,
+                            hold_producer: bool) -> bool:
+    """The tcgen05 product with every bounded wait cut to ``spin_limit`` polls and, if asked, a
+    producer that issues no copy: the consumers' waits then run out by construction, the launch
+    records the time-out in ``tc_status`` and returns.  For the tests of that path."""
+    m, n, k = _check_product(a, w, out, epilogue)
+    return library("fast").call_optional(
+        "bfi_gemm_tcgen05_bf16_wait_probe", _ptr(a), c_long(a.stride(0)), _ptr(w), c_long(w.stride(0)), _ptr(out),
+        c_int(dtype_code(out.dtype)), c_long(out.stride(0)), c_int(m), c_int(n), c_int(k), c_int(epilogue),
+        _ptr(tc_status(a.device)), c_int(int(spin_limit)), c_int(1 if hold_producer else 0), _stream())
+
+
 def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int) -> bool:
     """bfloat16 x bfloat16 -> ``out`` (float32 or bfloat16): the tcgen05 kernel, whose blocks start
     streaming W into their shared memory while the kernel before them still runs; the register-fed
@@ -125,12 +151,12 @@ def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
     return False
 
 
-def decode_splits(n_seqs: int, n_kv: int, group: int, max_pages: int) -> int:
+def decode_splits(n_seqs: int, n_kv: int, group: int, max_pages: int, n_sm: int) -> int:
     """Into how many page ranges every (sequence, kv head) is cut: enough blocks to fill the GPU
     once (two to three blocks are resident on an SM), never more than a sequence can have pages.
     Depends only on sizes that are fixed when a step is captured."""
     blocks = n_seqs * n_kv * ((group + 15) // 16)
-    want = (SM_COUNT * 5 // 2 + blocks - 1) // blocks
+    want = (n_sm * 5 // 2 + blocks - 1) // blocks
     return max(1, min(want, max_pages, 32))
 
 
@@ -140,7 +166,7 @@ def attention_decode_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads
         return False
     max_pages = kv.block_table.shape[1]
     group = n_heads // kv.n_kv_heads
-    max_splits = decode_splits(ctx.n_seqs, kv.n_kv_heads, group, max_pages)
+    max_splits = decode_splits(ctx.n_seqs, kv.n_kv_heads, group, max_pages, sm_count(qkv.device))
     part_o = part_ml = None
     if max_splits > 1:
         part_o = ctx.workspace.vector("attn.part_o", ctx.n_seqs * n_heads * max_splits * d, torch.float32)
@@ -182,3 +208,16 @@ def attention_prefill_tcgen05_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv
         _ptr(ctx.cu_seqlens), _ptr(ctx.seq_slot), _ptr(ctx.seq_start), c_int(ctx.n_seqs), c_long(qkv.shape[0]),
         c_int(ctx.max_seq_tokens), c_int(n_heads), c_int(kv.n_kv_heads), c_int(d), c_int(kv.window or 0), c_float(scale),
         _ptr(tc_status(qkv.device)), _stream())
+
+
+def attention_prefill_tcgen05_wait_probe(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float,
+                                         spin_limit: int, hold_producer: bool) -> bool:
+    """The tcgen05 prompt attention with its bounded waits cut to ``spin_limit`` polls and, if asked,
+    a producer warp that draws no item: see ``gemm_tcgen05_wait_probe``."""
+    return library("fast").call_optional(
+        "bfi_attention_prefill_tcgen05_bf16_wait_probe", _ptr(qkv), c_long(qkv.stride(0)), _ptr(out),
+        c_long(out.stride(0)), _ptr(kv.k), _ptr(kv.v), c_long(kv.k.shape[0]), _ptr(kv.block_table),
+        c_int(kv.block_table.stride(0)), _ptr(ctx.cu_seqlens), _ptr(ctx.seq_slot), _ptr(ctx.seq_start), c_int(ctx.n_seqs),
+        c_long(qkv.shape[0]), c_int(ctx.max_seq_tokens), c_int(n_heads), c_int(kv.n_kv_heads), c_int(kv.head_dim),
+        c_int(kv.window or 0), c_float(scale), _ptr(tc_status(qkv.device)), c_int(int(spin_limit)),
+        c_int(1 if hold_producer else 0), _stream())

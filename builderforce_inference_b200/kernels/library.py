@@ -19,6 +19,15 @@ class KernelError(RuntimeError):
 
 _lock = threading.Lock()
 _loaded: Dict[str, "KernelLibrary"] = {}
+_observer = None
+
+
+def set_call_observer(fn) -> None:
+    """``fn(function name, "begin" | "end")`` is called around every exported function that
+    launches (None: nobody watches).  The benchmark uses it to put CUDA events around each kernel
+    of one instrumented step; nothing on the product path sets it."""
+    global _observer
+    _observer = fn
 
 
 class KernelLibrary:
@@ -43,7 +52,11 @@ class KernelLibrary:
     def call_optional(self, func: str, *args) -> bool:
         """For kernels that may decline a shape: True if it ran, False if it declined (code 2)."""
         f = self._function(func)
+        if _observer is not None:
+            _observer(func, "begin")
         rc = f(*args)
+        if _observer is not None:
+            _observer(func, "end" if rc != 2 else "declined")
         if rc == 2:
             return False
         self.calls += 1
@@ -72,7 +85,11 @@ class KernelLibrary:
             f.restype = ctypes.c_int
             self._funcs[func] = f
         self.calls += 1
+        if _observer is not None:
+            _observer(func, "begin")
         rc = f(*args)
+        if _observer is not None:
+            _observer(func, "end")
         if rc != 0:
             raise KernelError(self.lib.bfi_last_error().decode("utf-8", "replace"))
 

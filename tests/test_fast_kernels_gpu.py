@@ -450,11 +450,9 @@ def test_gemm_tcgen05_many_tokens_every_tile(tile_n, halves, m, n, k, epi):
     import ctypes
     from builderforce_inference_b200.kernels.library import library
     lib = library("fast").lib
-    lib.bfi_gemm_tcgen05_tune_tile(ctypes.c_int(tile_n), ctypes.c_int(halves))
-    try:
-        tc_check(m, n, k, epi, seed=tile_n + halves)
-    finally:
-        lib.bfi_gemm_tcgen05_tune_tile(ctypes.c_int(0), ctypes.c_int(0))
+    # the override holds for the next call of the product only: nothing to put back
+    lib.bfi_gemm_tcgen05_tune_next(ctypes.c_int(0), ctypes.c_int(tile_n), ctypes.c_int(halves))
+    tc_check(m, n, k, epi, seed=tile_n + halves)
     assert tc_status_clear() == 0
 
 

@@ -76,13 +76,38 @@ def test_static_scratch_refuses_what_it_cannot_hold():
     assert _static(lib, a[:, :20], w[:, :20], out, 0) == 2          # K not a multiple of 8: declined
     # the library's own plans stay within the array; a plan forced to split K six ways over 299
     # tiles of 64 rows does not, and is refused before anything is launched
-    lib.bfi_skinny_tune(c_int(0), c_int(0), c_int(6))
-    try:
-        out.fill_(7.0)
-        assert _static(lib, a, w, out, 0) == 1
-        assert b"needs" in lib.bfi_last_error()
-        torch.cuda.synchronize()
-        assert float(out.min()) == 7.0 and float(out.max()) == 7.0
-    finally:
-        lib.bfi_skinny_tune(c_int(0), c_int(0), c_int(0))
-        fast_ops._plan_cache.clear()
+    out.fill_(7.0)
+    lib.bfi_skinny_tune_next(c_int(0), c_int(0), c_int(6))          # holds for the next call only
+    assert _static(lib, a, w, out, 0) == 1
+    assert b"needs" in lib.bfi_last_error()
+    torch.cuda.synchronize()
+    assert float(out.min()) == 7.0 and float(out.max()) == 7.0
+    # a wrong argument is refused before anything is put on the stream as well
+    assert _static(lib, a, w, out, 7) == 1 and b"epilogue" in lib.bfi_last_error()
+    # the override is gone: the same shape now runs with the library's own plan
+    assert _static(lib, a, w, out, 0) == 0
+    torch.cuda.synchronize()
+    assert float(out.abs().max()) == 0.0
+
+
+def test_static_scratch_entry_point_allocates_nothing():
+    """Device memory in use, as the driver counts it, is the same before and after a call (the
+    first call on a device has already looked the array's address up and loaded the kernels)."""
+    from builderforce_inference_b200.kernels import fast_ops
+    lib = _lib()
+    m, n, k = 8, 2560, 4096
+    assert fast_ops._skinny_scratch_need(m, n, k)[0] > 0
+    a = torch.randn(m, k).bfloat16().to(DEV)
+    w = torch.randn(n, k).bfloat16().to(DEV)
+    out = torch.zeros(m, n, dtype=torch.float32, device=DEV)
+    assert _static(lib, a, w, out, 1) == 0
+    torch.cuda.synchronize()
+
+    def free_bytes():
+        return torch.cuda.mem_get_info()[0]             # cudaMemGetInfo: what the driver has left
+
+    before, torch_before = free_bytes(), torch.cuda.memory_allocated()
+    for _ in range(3):
+        assert _static(lib, a, w, out, 1) == 0
+    torch.cuda.synchronize()
+    assert free_bytes() == before and torch.cuda.memory_allocated() == torch_before

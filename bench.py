@@ -4,10 +4,18 @@
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at the default batch (8), timed on
 the device over K single-token steps after W warm-up steps; ``e2e`` is the same through
-``Model.generate_batch`` with host token ids in and out; ``prefill`` is a 2,048-token prompt;
-``points`` holds decode at batch 1 and 64; ``roofline`` relates the decode step to the memory
-bandwidth.  The model has the layer sizes of the benchmark configuration with random weights and
-synthetic token ids; ``--layers`` runs fewer layers of the same sizes (``config`` names both).
+``Model.generate_batch`` with host token ids in and out (``e2e_b1``: at batch 1); ``prefill`` is a
+2,048-token prompt, with a breakdown of one instrumented step by kernel class; ``points`` holds
+decode at batch 1 and 64; ``decode_points`` holds, for batch 1, 8 and 64, a point right after the
+prompts (lengths uniform in [128, 2048]) and a point with every sequence at 4,080 to 4,096 tokens,
+the end of the benchmark's context, each with its step time, mean context, bytes and fraction of
+the memory bandwidth; ``roofline`` relates the main decode step to the memory bandwidth.  The model
+has the layer sizes of the benchmark configuration with random weights and synthetic token ids;
+``--layers`` runs fewer layers of the same sizes (``config`` names both).
+
+``--model 8b`` and ``--model 32b`` run the workloads named for those shapes instead (an unequal
+batch of 16 prompts of 64 to 4,096 tokens with 256 decode steps and an 8,192-token prompt; decode
+at batch 1 and 32 behind 2,048-token prompts and a 2,048-token prompt) and print one line each.
 
 The work is one GPU's: for ``--gpus`` above 1 it says so and exits with 2.  The reference arm
 (``--impl reference``) is unavailable: the reference is a Rust workspace, there is no Rust
@@ -112,14 +120,16 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def decode_run(model, batch, steps, warmup, seed):
-    """One varlen prefill (untimed), then warm-up and timed single-token steps; device-timed."""
+def decode_run(model, batch, steps, warmup, seed, lens=None):
+    """One varlen prefill (untimed), then warm-up and timed single-token steps; device-timed.
+    ``lens``: the prompts' lengths (default: uniform in [128, 2048])."""
     import torch
     from builderforce_inference_b200.engine.engine import SequenceStep
     eng = model.engine
     g = torch.Generator().manual_seed(seed)
     vocab = eng.spec.vocab_size
-    lens = torch.randint(128, 2049, (batch,), generator=g).tolist()
+    if lens is None:
+        lens = torch.randint(128, 2049, (batch,), generator=g).tolist()
     prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lens]
     slots = [eng.acquire() for _ in range(batch)]
     eng.step([SequenceStep(s, p, ()) for s, p in zip(slots, prompts)], check=False)
@@ -150,6 +160,15 @@ def decode_run(model, batch, steps, warmup, seed):
             "step_bytes": step_bytes, "ctx_mean": ctx_mean}
 
 
+def point(run, pk):
+    """A decode point as it goes into the line: rate, step time, mean context at the end of the
+    timed steps, the bytes a step has to read and their rate as a fraction of the copy bandwidth."""
+    gbs = run["step_bytes"] / (run["ms_per_step"] / 1e3) / 1e9
+    return {"tok_s": round(run["tok_s"], 1), "ms_per_step": round(run["ms_per_step"], 4),
+            "ctx_mean": round(run["ctx_mean"], 1), "step_bytes": int(run["step_bytes"]),
+            "gb_s": round(gbs, 1), "frac": round(gbs / pk["hbm_gbs"], 4)}
+
+
 def e2e_run(model, batch, steps, warmup, seed):
     """The same through ``Model.generate_batch``: host ids in, host ids out, every step."""
     import torch
@@ -170,32 +189,119 @@ def e2e_run(model, batch, steps, warmup, seed):
     return {"tok_s": tokens / (t1 - t0), "h2d": model.stepper.h2d_bytes, "d2h": model.stepper.d2h_bytes}
 
 
-def prefill_run(model, tokens, reps, layers, c=None):
+def prefill_flops(c, layers, lens):
+    """Floating-point operations of one prompt step over sequences of ``lens`` tokens, logits at
+    each sequence's last token."""
+    h, d, nq, nkv, inter = c["hidden_size"], c["head_dim"], c["num_attention_heads"], c["num_key_value_heads"], \
+        c["intermediate_size"]
+    tokens = sum(lens)
+    per_layer = 2 * tokens * (h * (nq + 2 * nkv) * d + nq * d * h + 3 * h * inter)
+    attn = sum(4 * nq * d * n * (n + 1) / 2 for n in lens)
+    return layers * (per_layer + attn) + 2 * h * c["vocab_size"] * len(lens)
+
+
+KERNEL_CLASSES = (("products", ("gemm", "skinny")), ("attention", ("attention",)))
+
+
+def prefill_breakdown(eng, step):
+    """One instrumented prompt step: a CUDA event before and after every kernel, so the kernels run
+    strictly one after the other (an event between two launches ends their overlap).  Returns the
+    milliseconds by kernel class, the time between kernels (the GPU waiting for the host), and the
+    whole of the instrumented step, which is therefore longer than a plain one."""
+    import torch
+    from builderforce_inference_b200.kernels import library as L
+    marks, open_ = [], []
+
+    def watch(name, what):
+        if what == "begin":
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            open_.append(e)
+        else:
+            e0 = open_.pop()
+            if what == "end":
+                e1 = torch.cuda.Event(enable_timing=True)
+                e1.record()
+                marks.append((name, e0, e1))
+
+    torch.cuda.synchronize()
+    L.set_call_observer(watch)
+    try:
+        step()
+    finally:
+        L.set_call_observer(None)
+    torch.cuda.synchronize()
+    out = {"products_ms": 0.0, "attention_ms": 0.0, "other_ms": 0.0}
+    for name, e0, e1 in marks:
+        cls = next((c for c, keys in KERNEL_CLASSES if any(k in name for k in keys)), "other")
+        out[cls + "_ms"] += e0.elapsed_time(e1)
+    whole = marks[0][1].elapsed_time(marks[-1][2]) if marks else 0.0
+    out["gaps_ms"] = max(0.0, whole - sum(out.values()))
+    out = {k: round(v, 3) for k, v in out.items()}
+    out["instrumented_ms"] = round(whole, 3)
+    out["kernels"] = len(marks)
+    return out
+
+
+def prefill_run(model, tokens, reps, layers, c=None, lens=None, breakdown=False):
     import torch
     from builderforce_inference_b200.engine.engine import SequenceStep
     eng = model.engine
     g = torch.Generator().manual_seed(99)
-    prompt = torch.randint(0, eng.spec.vocab_size, (tokens,), generator=g).tolist()
+    lens = lens or [tokens]
+    prompts = [torch.randint(0, eng.spec.vocab_size, (n,), generator=g).tolist() for n in lens]
     times = []
+
+    def run_once():
+        slots = [eng.acquire() for _ in prompts]
+        try:
+            eng.step([SequenceStep(s, p, (len(p) - 1,)) for s, p in zip(slots, prompts)], check=False)
+        finally:
+            torch.cuda.synchronize()
+            for s in slots:
+                eng.release(s)
+
     for i in range(reps + 2):
-        s = eng.acquire()
+        slots = [eng.acquire() for _ in prompts]
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         e0.record()
-        eng.step([SequenceStep(s, prompt, (tokens - 1,))], check=False)
+        eng.step([SequenceStep(s, p, (len(p) - 1,)) for s, p in zip(slots, prompts)], check=False)
         e1.record()
         torch.cuda.synchronize()
         if i >= 2:
             times.append(e0.elapsed_time(e1))
-        eng.release(s)
+        for s in slots:
+            eng.release(s)
     ms = statistics.median(times)
-    c = c or CONFIG_4B
-    h, d, nq, nkv, inter = c["hidden_size"], c["head_dim"], c["num_attention_heads"], c["num_key_value_heads"], \
-        c["intermediate_size"]
-    per_layer = 2 * tokens * (h * (nq + 2 * nkv) * d + nq * d * h + 3 * h * inter)
-    attn = 4 * nq * d * tokens * (tokens + 1) / 2
-    flops = layers * (per_layer + attn) + 2 * h * c["vocab_size"]
-    return {"ms": ms, "tok_s": tokens / (ms / 1e3), "flops": flops}
+    out = {"ms": ms, "tok_s": sum(lens) / (ms / 1e3), "flops": prefill_flops(c or CONFIG_4B, layers, lens)}
+    if breakdown:
+        out["breakdown"] = prefill_breakdown(eng, run_once)
+    return out
+
+
+def side_run(a, model, shape_cfg, pk) -> dict:
+    """The workloads named for the 8B and 32B shapes, beside the benchmark: one line of numbers."""
+    layers = a.layers
+    out = {}
+    if a.shape_name == "8b":
+        lens = [64 + round(i * (4096 - 64 - 300) / 15) for i in range(16)]      # 64 .. 3,796: room for 256 more
+        pf = prefill_run(model, 0, 3, layers, shape_cfg, lens=lens)
+        out["unequal16_prefill"] = {"tokens": sum(lens), "ms": round(pf["ms"], 3), "tok_s": round(pf["tok_s"], 1),
+                                    "frac": round(pf["flops"] / (pf["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+        decode_run(model, 16, 2, 3, seed=3, lens=lens)
+        out["unequal16_decode256"] = point(decode_run(model, 16, 256, 3, seed=4, lens=lens), pk)
+        pf = prefill_run(model, 8192, 3, layers, shape_cfg)
+        out["prefill_8192"] = {"tokens": 8192, "ms": round(pf["ms"], 3), "tok_s": round(pf["tok_s"], 1),
+                               "frac": round(pf["flops"] / (pf["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+    else:
+        for b in (1, 32):
+            decode_run(model, b, 2, 3, seed=3, lens=[2048] * b)
+            out[f"decode_b{b}_prompt2048"] = point(decode_run(model, b, 32, 3, seed=4, lens=[2048] * b), pk)
+        pf = prefill_run(model, 2048, 3, layers, shape_cfg)
+        out["prefill_2048"] = {"tokens": 2048, "ms": round(pf["ms"], 3), "tok_s": round(pf["tok_s"], 1),
+                               "frac": round(pf["flops"] / (pf["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+    return out
 
 
 KERNEL_SHAPES = {"qkv": (6144, 2560, 0), "o": (2560, 4096, 1), "gateup": (19456, 2560, 2), "down": (2560, 9728, 1),
@@ -364,9 +470,18 @@ def main() -> int:
     cfg = dict(shape_cfg, num_hidden_layers=a.layers)
     max_batch = a.batch if a.no_points else max(64, a.batch)
     t_load = time.time()
-    model = Model.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=max_batch * CONTEXT, max_seq_len=CONTEXT,
-                              max_batch=max_batch)
+    model = Model.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=max(max_batch * CONTEXT, 16384),
+                              max_seq_len=max(CONTEXT, 8192) if a.shape_name == "8b" else CONTEXT, max_batch=max_batch)
     print(f"[bench] model ready in {time.time() - t_load:.1f} s", file=sys.stderr, flush=True)
+
+    if a.shape_name != "4b":
+        clocks = ClockSampler()
+        clocks.start()
+        numbers = side_run(a, model, shape_cfg, pk)
+        print(json.dumps({"workloads": f"qwen3-{a.shape_name}-shape, builder-run beside the benchmark", "dtype": "bf16",
+                          "layers": a.layers, "layers_full": full_layers, "peaks": pk["source"], **numbers,
+                          "clocks": clocks.stop()}))
+        return 0
 
     # untimed: compile, capture graphs, size workspaces
     decode_run(model, a.batch, 2, 3, seed=1)
@@ -374,17 +489,28 @@ def main() -> int:
     clocks.start()
     main_run = decode_run(model, a.batch, a.steps, warmup, seed=2)
     e2e = e2e_run(model, a.batch, a.steps, warmup, seed=2)
-    points, prefill = {}, None
+    points, prefill, decode_points, e2e_b1 = {}, None, {}, None
     if not a.no_points:
-        for b in (1, 64):
+        deep_steps = 12                                   # 3 warm-up + 12 timed steps end at 4,095 of 4,096
+        deep_start = CONTEXT - (3 + deep_steps) - 1    # 4,080
+        for b in sorted({1, a.batch, 64}):
             if b == a.batch:
-                points[f"decode_b{b}"] = round(main_run["tok_s"], 1)
-                continue
-            decode_run(model, b, 2, 3, seed=3)
-            points[f"decode_b{b}"] = round(decode_run(model, b, min(a.steps, 32), warmup, seed=4)["tok_s"], 1)
-        pf = prefill_run(model, PREFILL_TOKENS, 5, a.layers, shape_cfg)
+                after = main_run
+            else:
+                decode_run(model, b, 2, 3, seed=3)         # untimed: graph capture for this batch size
+                after = decode_run(model, b, min(a.steps, 32), warmup, seed=4)
+            if b in (1, 64):
+                points[f"decode_b{b}"] = round(after["tok_s"], 1)
+            decode_points[f"b{b}_after_prompt"] = point(after, pk)
+            deep = decode_run(model, b, deep_steps, 3, seed=5, lens=[deep_start] * b)
+            decode_points[f"b{b}_ctx{CONTEXT}"] = point(deep, pk)
+        e1 = e2e_run(model, 1, min(a.steps, 32), warmup, seed=6)
+        e2e_b1 = {"value": round(e1["tok_s"], 1), "unit": "tokens/s", "h2d_bytes_per_step": e1["h2d"],
+                  "d2h_bytes_per_step": e1["d2h"]}
+        pf = prefill_run(model, PREFILL_TOKENS, 5, a.layers, shape_cfg, breakdown=True)
         prefill = {"value": round(pf["tok_s"], 1), "tokens": PREFILL_TOKENS, "ms": round(pf["ms"], 3),
-                   "frac": round(pf["flops"] / (pf["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+                   "frac": round(pf["flops"] / (pf["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+                   "breakdown": pf["breakdown"]}
     clk = clocks.stop()
 
     achieved = main_run["step_bytes"] / (main_run["ms_per_step"] / 1e3) / 1e9
@@ -411,6 +537,8 @@ def main() -> int:
     if prefill is not None:
         line["prefill"] = prefill
         line["points"] = points
+        line["decode_points"] = decode_points
+        line["e2e_b1"] = e2e_b1
     print(json.dumps(line))
     return 0
 

@@ -1,15 +1,23 @@
 """Command line, in the manner of the reference's ``bfi`` (crates/bfi/src/cli.rs:31-125):
 
     python -m builderforce_inference_b200 run   <model> [prompt]      one-shot, or a prompt loop without [prompt]
-    python -m builderforce_inference_b200 bench <model> --pp 512 --tg 128
+    python -m builderforce_inference_b200 bench <model> --pp 512 --tg 128 [--batch B --ctx C --reps R]
     python -m builderforce_inference_b200 random <config.json> <folder> --seed N
+    python -m builderforce_inference_b200 replay --model DIR --dtype D --out DIR --max-tokens N
 
-``<model>`` is a folder with config.json and model.safetensors.  A prompt is a list of token ids
-separated by spaces or commas (tokenizers are outside this library); generated ids are printed
-the same way.  ``run`` samples with the reference's defaults (greedy, 256 tokens:
+``<model>`` is a folder with config.json and model.safetensors, or, with ``--random-weights SEED``,
+a config.json whose model is made from that seed in device memory.  A prompt is a list of token ids
+separated by spaces or commas (tokenizers are outside this library), given on the command line or
+in a file (``--prompt-ids FILE``: one prompt per line, served as one batch); generated ids are
+printed the same way.  Stop ids come from the folder (generation_config.json, then config.json)
+unless ``--stop-id`` names them.  The cache is sized in tokens (``--max-tokens-cached``) or from a
+byte budget (``--cache-gib``).  ``run`` samples with the reference's defaults (greedy, 256 tokens:
 crates/bfi/src/commands.rs:79, crates/bfi-runtime/src/sample.rs:33-49) unless told otherwise.
 ``bench`` reports ``pp{N}`` and ``tg{N}`` tokens per second as a table
-(crates/bfi/src/commands.rs:250-294), timed on the device after a warm-up.
+(crates/bfi/src/commands.rs:250-294), timed on the device after a warm-up; ``--batch`` runs that many
+sequences together, ``--ctx`` starts the generation test from prompts of that length and ``--reps``
+repeats each test and reports the median.  ``replay`` is trace replay, the same code as
+``bin/trace_run``.
 """
 from __future__ import annotations
 
@@ -32,6 +40,10 @@ def _engine_flags(p: argparse.ArgumentParser) -> None:
     p.add_argument("--max-seq-len", type=int, default=None, help="cap on one sequence's context")
     p.add_argument("--max-tokens-cached", type=int, default=65536,
                    help="tokens the cache holds over all live sequences")
+    p.add_argument("--cache-gib", type=float, default=None,
+                   help="size the cache from this many GiB instead (keys, values and per-sequence state)")
+    p.add_argument("--random-weights", type=int, default=None, metavar="SEED",
+                   help="<model> is a config.json; make its weights from this seed instead of loading a folder")
     p.add_argument("--max-batch", type=int, default=64)
     p.add_argument("--device", default="cuda:0")
 
@@ -59,14 +71,35 @@ def _params(a):
 
 def _load(a):
     from .engine.api import Model
+    kw = dict(dtype=a.dtype, max_tokens=a.max_tokens_cached, max_seq_len=a.max_seq_len, max_batch=a.max_batch,
+              device=a.device)
+    if a.cache_gib is not None:
+        kw.update(cache_bytes=int(a.cache_gib * (1 << 30)), cache_slots=a.max_batch)
+    if a.random_weights is not None:
+        from .config import read_json
+        print(f"random weights for {a.model}, seed {a.random_weights}", file=sys.stderr, flush=True)
+        return Model.from_random(read_json(a.model), a.random_weights, **kw)
     print(f"loading {a.model}", file=sys.stderr, flush=True)
-    return Model.load(a.model, dtype=a.dtype, max_tokens=a.max_tokens_cached, max_seq_len=a.max_seq_len,
-                      max_batch=a.max_batch, device=a.device)
+    return Model.load(a.model, **kw)
+
+
+def _prompts_of_file(path: str):
+    with open(path, "r", encoding="utf-8") as f:
+        prompts = [_ids(line) for line in f if line.strip()]
+    if not prompts:
+        raise SystemExit(f"{path}: no prompt (one list of token ids per line)")
+    return prompts
 
 
 def cmd_run(a) -> int:
+    if a.prompt is not None and a.prompt_ids is not None:
+        raise SystemExit("give a prompt on the command line or --prompt-ids FILE, not both")
     model = _load(a)
     params = _params(a)
+    if a.prompt_ids is not None:
+        for out in model.generate_batch(_prompts_of_file(a.prompt_ids), params, a.stop_id, a.ignore_eos):
+            print(" ".join(str(t) for t in out))
+        return 0
     if a.prompt is not None:
         out = model.generate(_ids(a.prompt), params, a.stop_id, a.ignore_eos)
         print(" ".join(str(t) for t in out))
@@ -87,27 +120,38 @@ def cmd_run(a) -> int:
 
 
 def cmd_bench(a) -> int:
+    import statistics
+
     import torch
     from .sampling import SampleParams
     model = _load(a)
     vocab = model.n_vocab()
     g = torch.Generator().manual_seed(0)
-    pp_prompt = torch.randint(0, vocab, (max(a.pp, 1),), generator=g).tolist()
-    tg_prompt = torch.randint(0, vocab, (2,), generator=g).tolist()
+    batch, reps = max(a.batch, 1), max(a.reps, 1)
 
-    def timed(prompt, n_new):
-        model.generate(prompt, SampleParams(max_tokens=n_new), ignore_eos=True)       # warm-up
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        model.generate(prompt, SampleParams(max_tokens=n_new), ignore_eos=True)
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / 1e3
+    def prompts(n):
+        return [torch.randint(0, vocab, (max(n, 1),), generator=g).tolist() for _ in range(batch)]
 
-    pp_s = timed(pp_prompt, 1)
-    tg_s = timed(tg_prompt, a.tg)
-    label = f"B200 sm_100a {a.dtype}"
-    rows = [("pp%d" % a.pp, a.pp / pp_s), ("tg%d" % a.tg, a.tg / tg_s)]
+    pp_prompts = prompts(a.pp)
+    tg_prompts = prompts(a.ctx if a.ctx else 2)
+
+    def timed(ps, n_new):
+        model.generate_batch(ps, SampleParams(max_tokens=n_new), ignore_eos=True)       # warm-up
+        times = []
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            model.generate_batch(ps, SampleParams(max_tokens=n_new), ignore_eos=True)
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1) / 1e3)
+        return statistics.median(times)
+
+    pp_s = timed(pp_prompts, 1)
+    # generation is timed without its prompts: the same prompts with one new token are taken off
+    tg_s = timed(tg_prompts, a.tg + 1) - timed(tg_prompts, 1)
+    label = f"B200 sm_100a {a.dtype}" + (f" b{batch}" if batch > 1 else "") + (f" ctx{a.ctx}" if a.ctx else "")
+    rows = [("pp%d" % a.pp, batch * a.pp / pp_s), ("tg%d" % a.tg, batch * a.tg / max(tg_s, 1e-9))]
     if a.json:
         print(json.dumps({name: ts for name, ts in rows}))
         return 0
@@ -116,6 +160,11 @@ def cmd_bench(a) -> int:
     for name, ts in rows:
         print(f"| {a.model} | {label} | {name} | {ts:.2f} |")
     return 0
+
+
+def cmd_replay(a) -> int:
+    from .engine.replay import replay
+    return replay(a)
 
 
 def cmd_random(a) -> int:
@@ -135,6 +184,8 @@ def main(argv=None) -> int:
     r = sub.add_parser("run", help="generate for one prompt, or read prompts line by line")
     r.add_argument("model")
     r.add_argument("prompt", nargs="?", default=None)
+    r.add_argument("--prompt-ids", default=None, metavar="FILE",
+                   help="prompts from a file, one list of token ids per line, served as one batch")
     _engine_flags(r)
     _sample_flags(r)
     r.set_defaults(fn=cmd_run)
@@ -143,6 +194,9 @@ def main(argv=None) -> int:
     b.add_argument("--pp", type=int, default=512)
     b.add_argument("--tg", type=int, default=128)
     b.add_argument("--json", action="store_true")
+    b.add_argument("--batch", type=int, default=1, help="sequences run together")
+    b.add_argument("--ctx", type=int, default=0, help="generate from prompts of this many tokens (0: two tokens)")
+    b.add_argument("--reps", type=int, default=1, help="timed repetitions of each test (the median is reported)")
     _engine_flags(b)
     b.set_defaults(fn=cmd_bench)
     w = sub.add_parser("random", help="write a model folder with random weights")
@@ -151,6 +205,10 @@ def main(argv=None) -> int:
     w.add_argument("--seed", type=int, default=0)
     w.add_argument("--store-dtype", default="bfloat16", choices=["bfloat16", "float32"])
     w.set_defaults(fn=cmd_random)
+    t = sub.add_parser("replay", help="trace replay: token ids step by step from standard input, logits to files")
+    from .engine.replay import add_arguments
+    add_arguments(t)
+    t.set_defaults(fn=cmd_replay)
     a = ap.parse_args(argv)
     return a.fn(a)
 

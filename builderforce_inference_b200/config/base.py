@@ -113,3 +113,16 @@ def read_json(path: str) -> Dict[str, Any]:
             return json.load(f)
         except json.JSONDecodeError as e:
             raise ConfigError(f"{path}: not valid JSON ({e})") from e
+
+
+def stop_ids_of_folder(folder: str, from_config: Iterable[int]) -> tuple:
+    """The stop token ids of a model folder: those of ``generation_config.json`` (key
+    ``eos_token_id``, an id or a list) when that file is there, followed by the ones config.json
+    names that it does not repeat; config.json's alone otherwise.  The reference takes its end
+    token from the model file's metadata as well (crates/bfi-runtime/src/tokenize.rs:68)."""
+    ids = list(from_config)
+    path = os.path.join(folder, "generation_config.json")
+    if os.path.isfile(path):
+        first = list(ConfigReader(read_json(path), path).int_or_list("eos_token_id"))
+        ids = first + [i for i in ids if i not in first]
+    return tuple(ids)

@@ -109,6 +109,12 @@ class Qwen3Config:
                 raise ConfigError(f"{what}: 'use_sliding_window' is true but 'sliding_window' is null")
             if kinds is not None:
                 windows = tuple(window if k == "sliding_attention" else None for k in kinds)
+            elif not r.has("max_window_layers"):
+                # the usual tooling fills this key with a fixed default of its own; guessing one
+                # here would silently window other layers than the writer of the file meant
+                raise ConfigError(
+                    f"{what}: 'use_sliding_window' is true but neither 'layer_types' nor "
+                    f"'max_window_layers' says which layers are windowed")
             else:
                 windows = tuple(window if i >= first_windowed else None for i in range(n_layer))
         elif kinds is not None and any(k == "sliding_attention" for k in kinds):

@@ -80,7 +80,7 @@ class Model:
         self.engine = engine
         self.max_batch = max_batch
         self.stepper = EngineStepper(engine)
-        self.stop_ids = tuple(engine.spec.stop_ids)
+        self.stop_ids = tuple(engine.stop_ids)
         self.last_generated_tokens = 0
         self.last_batch_decode_steps = 0
         self.last_finish_reasons: List[str] = []

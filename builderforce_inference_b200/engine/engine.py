@@ -24,7 +24,8 @@ import torch
 
 from ..cache.cache import SequenceCache
 from ..cache.pages import PAGE_TOKENS, CacheError
-from ..config.base import read_json
+from ..cache.plan import plan_cache
+from ..config.base import read_json, stop_ids_of_folder
 from ..kernels import ops
 from ..kernels.library import total_calls
 from ..parts.base import ModelSpec
@@ -67,6 +68,43 @@ def pack_meta(dst: np.ndarray, tok, pos, slot_of, cu, n_tok: int, n_seq: int, se
     o += 1
     dst[o:o + len(want_rows)] = want_rows
     return o + len(want_rows)
+
+
+
+class PinnedRings:
+    """Page-locked staging buffers for the steps' index arrays: ``PINNED_RING`` buffers in rotation
+    per capacity, capacities being powers of two (at least ``MIN_CAPACITY`` values).  However many
+    distinct lengths are asked for, at most ``PINNED_RING * log2(largest / MIN_CAPACITY)`` buffers
+    ever exist.  An entry is ``[buffer, event]``; ``take`` waits for the event of the entry it hands
+    out, so a buffer is never rewritten while a copy still reads it."""
+
+    MIN_CAPACITY = 64
+
+    def __init__(self, make=None):
+        self._rings: Dict[int, dict] = {}
+        self._make = make or (lambda cap: torch.empty(cap, dtype=torch.int32, pin_memory=True))
+
+    @classmethod
+    def capacity_for(cls, n: int) -> int:
+        cap = cls.MIN_CAPACITY
+        while cap < n:
+            cap *= 2
+        return cap
+
+    def take(self, n: int) -> list:
+        ring = self._rings.setdefault(self.capacity_for(n), {"next": 0, "slots": []})
+        if len(ring["slots"]) < PINNED_RING:
+            ring["slots"].append([self._make(self.capacity_for(n)), None])
+            return ring["slots"][-1]
+        entry = ring["slots"][ring["next"]]
+        ring["next"] = (ring["next"] + 1) % PINNED_RING
+        if entry[1] is not None:
+            entry[1].synchronize()
+        return entry
+
+    def n_buffers(self) -> int:
+        return sum(len(r["slots"]) for r in self._rings.values())
+
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 
@@ -133,27 +171,37 @@ class Engine:
     def __init__(self, spec: ModelSpec, tensors: Dict[str, torch.Tensor], dtype: torch.dtype,
                  device: torch.device, max_tokens: int, max_seq_len: Optional[int] = None,
                  use_graphs: bool = True, prefill_chunk_tokens: int = 8192,
-                 config: Optional[Dict[str, Any]] = None):
+                 config: Optional[Dict[str, Any]] = None, cache_bytes: Optional[int] = None,
+                 cache_slots: int = 64):
+        """``max_tokens`` sizes the cache in tokens (summed over live sequences, each rounded up to
+        a page).  ``cache_bytes``, when given, sizes it from a byte budget instead: the tokens that
+        fit beside the fixed-size state of ``cache_slots`` sequences (``cache.plan.plan_cache``)."""
         _require_gpu(device)
         self.spec = spec
         self.config = config
         self.dtype = dtype
         self.device = device
+        self.runtime = Runtime(device, dtype)
+        self.decoder = Decoder(spec, self.runtime)
+        self.stop_ids = tuple(spec.stop_ids)      # a loaded folder may add its generation_config.json's
+        self.cache_plan = None
+        if cache_bytes is not None:
+            self.cache_plan = plan_cache(self.decoder.run_needs(), self.decoder.run_cache_of(), int(cache_bytes),
+                                         2 if dtype == torch.bfloat16 else 4, cache_slots)
+            max_tokens = self.cache_plan.max_tokens
         limit = spec.max_positions if spec.max_positions > 0 else max_tokens
         self.max_seq_len = min(limit, max_seq_len) if max_seq_len else limit
         self.max_seq_len = max(1, min(self.max_seq_len,
                                       ((max_tokens + PAGE_TOKENS - 1) // PAGE_TOKENS) * PAGE_TOKENS))
-        self.runtime = Runtime(device, dtype)
-        self.decoder = Decoder(spec, self.runtime)
         self.decoder.load(tensors, self.max_seq_len)
         self.cache = SequenceCache(self.decoder.run_needs(), self.decoder.run_cache_of(), max_tokens,
-                                   self.max_seq_len, dtype, device)
+                                   self.max_seq_len, dtype, device, initial_slots=max(1, int(cache_slots)))
         self.workspace = Workspace(device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.prefill_chunk_tokens = max(PAGE_TOKENS, int(prefill_chunk_tokens))
         self.use_graphs = bool(use_graphs) and self.decoder.graph_safe()
         self._graphs: Dict[int, _DecodeGraph] = {}
-        self._pinned: Dict[int, dict] = {}
+        self._pinned = PinnedRings()
         self.last_h2d_bytes = 0        # bytes of index arrays the last step copied to the device
         self.graph_kernel_launches = 0  # kernels launched through graph replays so far
 
@@ -168,7 +216,9 @@ class Engine:
         config = read_json(os.path.join(folder, "config.json"))
         spec = describe_model(config)
         tensors = load_folder(folder, expected_tensors(spec), spec.ignored_names, dt, dev)
-        return cls(spec, tensors, dt, dev, max_tokens, max_seq_len, config=config, **kw)
+        eng = cls(spec, tensors, dt, dev, max_tokens, max_seq_len, config=config, **kw)
+        eng.stop_ids = stop_ids_of_folder(folder, spec.stop_ids)
+        return eng
 
     @classmethod
     def from_random(cls, config: Dict[str, Any], seed: int, dtype="bfloat16", max_tokens: int = 16384,
@@ -190,6 +240,15 @@ class Engine:
 
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
+
+    def rewind(self, slot: int, length: int) -> None:
+        """Keep only the first ``length`` tokens of the sequence in ``slot``; the next step goes on
+        from there (crates/bfi-models/src/session.rs:50-62).  Refused by name for models with
+        windowed layers or per-sequence state of fixed size."""
+        try:
+            self.cache.rewind(slot, length)
+        except CacheError as e:
+            raise StepError(str(e)) from e
 
     # ---- the step function -----------------------------------------------------------
     def step(self, seqs: Sequence[SequenceStep], check: bool = True) -> torch.Tensor:
@@ -386,21 +445,15 @@ class Engine:
         pages = sum((int(st) + (int(cu[i + 1]) - int(cu[i])) + PAGE_TOKENS - 1) // PAGE_TOKENS
                     for i, st in enumerate(seq_starts))
         n = self._meta_len(n_tok, n_seq, len(want_rows))
-        # a ring of pinned staging buffers per size: a buffer is rewritten only after the copy that
-        # last read it has completed (its event), which with four in rotation was steps ago, so the
-        # host packs the next step while the GPU still runs this one
-        ring = self._pinned.setdefault(n, {"next": 0, "slots": []})
-        if len(ring["slots"]) < PINNED_RING:
-            ring["slots"].append([torch.empty(n, dtype=torch.int32, pin_memory=True), None])
-            entry = ring["slots"][-1]
-        else:
-            entry = ring["slots"][ring["next"]]
-            ring["next"] = (ring["next"] + 1) % PINNED_RING
-            if entry[1] is not None:
-                entry[1].synchronize()
+        # a ring of pinned staging buffers per capacity (the next power of two at or above the
+        # length, so the number of rings is bounded whatever lengths the steps have): a buffer is
+        # rewritten only after the copy that last read it has completed (its event), which with
+        # four in rotation was steps ago, so the host packs the next step while the GPU still
+        # runs this one
+        entry = self._pinned.take(n)
         pinned = entry[0]
         pack_meta(pinned.numpy(), tok, pos, slot_of, cu, n_tok, n_seq, seq_slots, seq_starts, pages, want_rows)
-        meta[:n].copy_(pinned, non_blocking=True)
+        meta[:n].copy_(pinned[:n], non_blocking=True)
         if entry[1] is None:
             entry[1] = torch.cuda.Event()
         entry[1].record(torch.cuda.current_stream(self.device))

@@ -126,7 +126,9 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     def cache_need(self):
-        """``KVNeed``, ``StateNeed`` or None."""
+        """What the mixer keeps per sequence: ``KVNeed``, ``StateNeed``, None, or a tuple of several
+        (keys and values beside a fixed-size state, say).  The run's cache then carries one entry
+        per need, in this order, in ``run.entries``."""
         return None
 
     def prepare(self, runtime, max_positions: int) -> None:

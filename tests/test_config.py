@@ -53,6 +53,7 @@ def test_missing_required_key_is_named(key):
     ({"rms_norm_eps": -1.0}, "rms_norm_eps"),
     ({"head_dim": 15}, "head_dim"),
     ({"use_sliding_window": True, "sliding_window": None}, "sliding_window"),
+    ({"use_sliding_window": True, "sliding_window": 32}, "max_window_layers"),
     ({"layer_types": ["full_attention"]}, "layer_types"),
 ])
 def test_unsupported_options_are_refused_by_name(patch, word):

@@ -174,23 +174,108 @@ def test_first_tokens_of_a_sequence(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_poisoned_cache_and_stale_rows_do_not_matter(dtype):
+@pytest.mark.parametrize("name", ["A", "E", "F"])
+def test_poisoned_cache_and_stale_rows_do_not_matter(name, dtype):
     """Every page is filled with NaN before use: rows at or past a sequence's length, and rows a
-    freed slot left behind, are never read."""
-    name = "A"
-    eng = load(name, dtype, max_tokens=64 * 4)
+    freed slot left behind, are never read.  E and F have the head sizes of the bfloat16 decode
+    and prompt attention kernels (64 with a window of 70, and 128); their prompts are long enough
+    for the tensor-core prompt kernel (128 tokens and more in one step)."""
+    long = name != "A"
+    n1, n2, k2 = (330, 300, 140) if long else (70, 45, 30)
+    eng = load(name, dtype, max_tokens=64 * (8 if long else 4))
     folder = model_folder(name, store_dtype(dtype))
     eng.cache.poison()
-    p1, p2 = random_prompts(CONFIGS[name]["vocab_size"], [70, 45], seed=4)
+    p1, p2 = random_prompts(CONFIGS[name]["vocab_size"], [n1, n2], seed=4)
     s = eng.acquire()
-    check(eng.step([S(s, p1, list(range(70)))]).cpu(), plain_logits(folder, p1), dtype, "first use")
+    check(eng.step([S(s, p1, list(range(n1)))]).cpu(), plain_logits(folder, p1), dtype, "first use")
     eng.release(s)
     s2 = eng.acquire()
     assert s2 == s
-    got = [eng.step([S(s2, p2[:30], list(range(30)))]).cpu().clone()]
-    for t in p2[30:]:
+    got = [eng.step([S(s2, p2[:k2], list(range(k2)))]).cpu().clone()]
+    for t in p2[k2:k2 + 20]:
         got.append(eng.step([S(s2, [t], [0])]).cpu().clone())
+    rest = p2[k2 + 20:]                         # a continuation of 140 tokens over the stale rows
+    got.append(eng.step([S(s2, rest, list(range(len(rest))))]).cpu().clone())
     check(torch.cat(got), plain_logits(folder, p2), dtype, "reused slot over stale rows")
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["E", "F"])
+def test_long_continuations_through_the_fast_attention(name, dtype):
+    """Pieces of 128 tokens and more that continue a cached prefix (the tensor-core prompt kernel
+    with a start above zero), through the engine's own cache: for E the windowed layer (70 keys)
+    has by then given back the pages behind its window, so the kernel meets their -1 entries; a
+    neighbour of another phase shares the steps; single tokens in between."""
+    folder = model_folder(name, store_dtype(dtype))
+    p, q = random_prompts(CONFIGS[name]["vocab_size"], [500, 260], seed=16)
+    rp, rq = plain_logits(folder, p), plain_logits(folder, q)
+    eng = load(name, dtype)
+    eng.cache.poison()
+    a, b = eng.acquire(), eng.acquire()
+    cuts_a, cuts_b = [0, 1, 70, 200, 201, 372, 500], [0, 130, 131, 260]
+    ga, gb = [], []
+    for step in range(6):
+        seqs = []
+        if step + 1 < len(cuts_a):
+            ta = p[cuts_a[step]:cuts_a[step + 1]]
+            seqs.append(S(a, ta, list(range(len(ta)))))
+        if step + 1 < len(cuts_b):
+            tb = q[cuts_b[step]:cuts_b[step + 1]]
+            seqs.append(S(b, tb, list(range(len(tb)))))
+        lg = eng.step(seqs).cpu().clone()
+        if step + 1 < len(cuts_a):
+            ga.append(lg[:len(ta)])
+            lg = lg[len(ta):]
+        if step + 1 < len(cuts_b):
+            gb.append(lg)
+    bad = first_bad_row(torch.cat(ga), rp, dtype)
+    assert bad is None, f"request a: first wrong position {bad} (pieces start at {cuts_a})"
+    bad = first_bad_row(torch.cat(gb), rq, dtype)
+    assert bad is None, f"request b: first wrong position {bad} (pieces start at {cuts_b})"
+    if CONFIGS[name].get("use_sliding_window"):
+        win = [g for g in eng.cache.kv_groups if g.need.window is not None][0]
+        assert win.table.rows[a][:6] == [-1] * 6          # pages behind the window went back
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_rewind_and_redo(name, dtype):
+    """A sequence wound back to a shorter prefix and continued gives what the whole gives
+    (crates/bfi-models/src/session.rs:50-62); the pages past the mark are free meanwhile."""
+    from builderforce_inference_b200.engine.engine import StepError
+    folder = model_folder(name, store_dtype(dtype))
+    n = 120 if name == "A" else 200
+    p, other = random_prompts(CONFIGS[name]["vocab_size"], [n, n], seed=12)
+    ref = plain_logits(folder, p)
+    eng = load(name, dtype, max_tokens=64 * 8)
+    eng.cache.poison()
+    s = eng.acquire()
+    k = n - 50
+    eng.step([S(s, p[:k], [])])
+    for t in other[:7]:                                  # tokens that will be wound back
+        eng.step([S(s, [t], [0])])
+    held = eng.cache.kv_groups[0].table.held_pages()
+    eng.rewind(s, 40)
+    assert eng.length(s) == 40 and eng.cache.kv_groups[0].table.held_pages() == 1 < held
+    got = eng.step([S(s, p[40:k], list(range(k - 40)))]).cpu().clone()
+    check(got, ref[40:k], dtype, "redo after rewind")
+    rows = [eng.step([S(s, [t], [0])]).cpu().clone() for t in p[k:k + 5]]
+    eng.rewind(s, k + 2)
+    rows = rows[:2] + [eng.step([S(s, [t], [0])]).cpu().clone() for t in p[k + 2:]]
+    check(torch.cat(rows), ref[k:], dtype, "single tokens after a rewind")
+    eng.rewind(s, 0)
+    check(eng.step([S(s, p[:33], list(range(33)))]).cpu(), ref[:33], dtype, "from the start again")
+    with pytest.raises(StepError, match="cannot keep"):
+        eng.rewind(s, 34)
+    eng.release(s)
+    eng.cache.check()
+    windowed = load("C", dtype)
+    s = windowed.acquire()
+    windowed.step([S(s, [1, 2, 3], [])])
+    with pytest.raises(StepError, match="rewind unsupported"):
+        windowed.rewind(s, 1)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -318,3 +403,45 @@ def test_benchmark_layer_sizes_against_plain(dtype):
         for j in (0, 1, 2, 3, 20, 39):
             e = rel_err(lg[j:j + 1], refs[src[j]][pre[j] + step:pre[j] + step + 1])
             assert e < tol(dtype), f"batch of 40, row {j}, step {step}: rel err {e:.3e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_the_benchmark_lengths_against_plain(dtype):
+    """Two layers at the Qwen3-4B widths at the lengths the benchmark runs: a 2,048-token prompt
+    whole (16 tiles of 128 tokens per head); the same cut 1,000 + 1,048 (a long continuation);
+    single tokens at positions 4,088 to 4,095 alone (64 pages, the most page ranges per sequence)
+    and inside unequal batches of 8 and of 40.  Every sequence is a prefix of one 4,096-token
+    prompt, so one run of the plain implementation serves them all."""
+    name = "WIDE"
+    folder = model_folder(name, store_dtype(dtype))
+    full = random_prompts(CONFIGS[name]["vocab_size"], [4096], seed=77)[0]
+    ref = plain_logits(folder, full)
+    eng = load(name, dtype, max_tokens=64 * 600, prefill_chunk_tokens=4096)
+    eng.cache.poison()
+    s = eng.acquire()
+    got = eng.step([S(s, full[:2048], list(range(2048)))]).cpu()
+    bad = first_bad_row(got, ref[:2048], dtype)
+    assert bad is None, f"2,048 tokens whole: first wrong position {bad}"
+    eng.release(s)
+    s = eng.acquire()
+    got = [eng.step([S(s, full[:1000], list(range(990, 1000)))]).cpu().clone()]
+    got.append(eng.step([S(s, full[1000:2048], list(range(1048)))]).cpu().clone())
+    bad = first_bad_row(torch.cat(got), ref[990:2048], dtype)
+    assert bad is None, f"1,000 + 1,048: first wrong position {990 + bad}"
+    # go on to 4,088 (a continuation of 2,040 tokens) and decode the last 8 alone
+    eng.step([S(s, full[2048:4088], [])])
+    rows = [eng.step([S(s, [full[t]], [0])]).cpu().clone() for t in range(4088, 4096)]
+    check(torch.cat(rows), ref[4088:], dtype, "positions 4,088..4,095 alone")
+    eng.release(s)
+    for batch in (8, 40):
+        lens = [4088] + [1 + (i * 397) % 700 for i in range(1, batch - 1)] + [2047]
+        slots = [eng.acquire() for _ in lens]
+        eng.step([S(sl, full[:n], []) for sl, n in zip(slots, lens)])
+        for step in range(8):
+            lg = eng.step([S(sl, [full[n + step]], [0]) for sl, n in zip(slots, lens)]).cpu()
+            for j in (0, 1, batch // 2, batch - 1):
+                e = rel_err(lg[j:j + 1], ref[lens[j] + step:lens[j] + step + 1])
+                assert e < tol(dtype), f"batch of {batch}, row {j} (position {lens[j] + step}): rel err {e:.3e}"
+        for sl in slots:
+            eng.release(sl)
+    eng.cache.check()

@@ -1,5 +1,8 @@
 """Generation through the Python entry point and the command line against the plain
 implementation: greedy ids, stop tokens, unequal batches, seeded temperature sampling."""
+import json
+import math
+import os
 import subprocess
 import sys
 
@@ -18,22 +21,32 @@ def load(name, dtype, **kw):
     return Model.load(model_folder(name, store_dtype(dtype)), dtype=dtype, **kw)
 
 
-def plain_greedy_with_margin(folder, prompt, got, stop=()):
-    """Walk the plain implementation along the engine's tokens: each must be the plain argmax, or
-    lie within ``margin`` of it (bfloat16 may swap near-ties; float32 gets no slack to speak of)."""
+NEAR_TIE = 1e-2      # of max |logit|: a plain top-2 gap below this may flip under bfloat16 rounding
+
+
+def walk_plain_greedy(folder, prompt, got):
+    """Walk the plain implementation along the engine's tokens.  Returns the steps at which the
+    engine's token is not the plain argmax, each with the gap between the plain best logit and the
+    engine's choice, as a fraction of the largest |logit| of that step."""
     cfg, w = plain_model(folder)
     ids = list(prompt)
-    margins = []
-    for tok in got:
+    swaps = []
+    for step, tok in enumerate(got):
         logits = P.forward_each(w, cfg, ids)[-1]
-        margins.append(float(logits.max() - logits[tok]))
+        if tok != P.argmax_first(logits.tolist()):
+            swaps.append((step, float(logits.max() - logits[tok]) / float(logits.abs().max())))
         ids.append(tok)
-    return margins
+    return swaps
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_greedy_batch_matches_plain(name, dtype):
+    """32 greedy tokens per request.  float32: the plain implementation's ids exactly.  bfloat16:
+    the same ids (the reference asks for exact top-1 agreement, crates/bfi-runtime/tests/
+    golden_greedy.rs:102-144), except at steps where the plain top-2 gap is a near-tie, and those
+    are counted: from a swap on, the walk follows the engine's token, so later steps are judged on
+    the engine's own prefix."""
     model = load(name, dtype)
     folder = model_folder(name, store_dtype(dtype))
     cfg, w = plain_model(folder)
@@ -42,16 +55,23 @@ def test_greedy_batch_matches_plain(name, dtype):
     prompts = random_prompts(CONFIGS[name]["vocab_size"], lens, seed=3)
     outs = model.generate_batch(prompts, SampleParams(max_tokens=32), ignore_eos=True)
     assert model.last_batch_decode_steps == 31 and model.last_generated_tokens == 32 * len(prompts)
+    n_swaps = 0
     for p, got in zip(prompts, outs):
         assert len(got) == 32
         if dtype == "float32":
             assert got == P.greedy_generate(w, cfg, p, 32)
         else:
-            scale = float(P.forward_each(w, cfg, p)[-1].abs().max())
-            assert max(plain_greedy_with_margin(folder, p, got)) < 2e-2 * scale
+            swaps = walk_plain_greedy(folder, p, got)
+            assert all(gap < NEAR_TIE for _, gap in swaps), swaps
+            n_swaps += len(swaps)
+    # near-ties that bfloat16 rounding turned, over all requests and steps of this configuration
+    assert n_swaps <= MAX_BF16_SWAPS[name], n_swaps
     # alone, each request generates what it generated in the batch
     for p, got in zip(prompts[:2], outs[:2]):
         assert model.generate(p, SampleParams(max_tokens=32), ignore_eos=True) == got
+
+
+MAX_BF16_SWAPS = {"A": 2, "B": 3}     # of 96 and 128 steps
 
 
 def test_stop_tokens_budgets_and_reuse():
@@ -120,6 +140,46 @@ def test_sampling_is_seeded_and_follows_the_plain_distribution(params):
             ids.append(tok)
 
 
+def test_seeded_temperature_sampling_in_bfloat16():
+    """Tiny B at temperature 0.8, seeded, in bfloat16.  The engine's logits differ from the plain
+    ones by at most e = BF16_TOL * max|logit|, so every probability moves by a factor within
+    exp(+-2e/T) and the cumulative distribution by at most d = exp(2e/T) - 1 anywhere: the sampled
+    token's plain interval, widened by d, must hold the uniform number.  Most tokens must be the
+    plain sampler's exact choice."""
+    from builderforce_inference_b200 import SampleParams
+    from builderforce_inference_b200.sampling import uniform_draw
+    from helpers import BF16_TOL
+    import math
+    model = load("B", "bfloat16")
+    cfg, w = plain_model(model_folder("B", torch.bfloat16))
+    prompts = random_prompts(384, [1, 7, 32, 64], seed=8)
+    sp = SampleParams(max_tokens=16, temperature=0.8, seed=5)
+    outs = model.generate_batch(prompts, sp, ignore_eos=True)
+    assert outs == model.generate_batch(prompts, sp, ignore_eos=True)
+    exact = total_tokens = 0
+    pp = P.PlainSampleParams(temperature=0.8, seed=5)
+    for r, (p, got) in enumerate(zip(prompts, outs)):
+        ids = list(p)
+        assert len(got) == 16
+        for step, tok in enumerate(got):
+            logits = P.forward_each(w, cfg, ids)[-1]
+            kind, val = P.target(logits.tolist(), ids, pp)
+            assert kind == "weights"
+            u = uniform_draw(sp.seed, r, step)
+            total = sum(pr for _, pr in val)
+            d = math.exp(2.0 * BF16_TOL * float(logits.abs().max()) / 0.8) - 1.0
+            cum, ok = 0.0, False
+            for i, pr in val:
+                lo, cum = cum, cum + pr
+                if i == tok:
+                    ok = lo / total - d <= u <= cum / total + d
+                    exact += int(P.draw(val, u) == tok)
+            assert ok, (r, step, tok, d)
+            total_tokens += 1
+            ids.append(tok)
+    assert exact >= 0.9 * total_tokens, (exact, total_tokens)
+
+
 def test_command_line_run_and_bench():
     folder = model_folder("A", torch.float32)
     cfg, w = plain_model(folder)
@@ -133,3 +193,63 @@ def test_command_line_run_and_bench():
                         "16", "--dtype", "bfloat16"], cwd=ROOT, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stderr[-2000:]
     assert "| pp64 |" in r.stdout and "| tg16 |" in r.stdout
+    rates = [float(line.split("|")[4]) for line in r.stdout.splitlines() if "| pp64 |" in line or "| tg16 |" in line]
+    assert len(rates) == 2 and all(math.isfinite(x) and x > 0 for x in rates), r.stdout
+    r = subprocess.run([sys.executable, "-m", "builderforce_inference_b200", "bench", folder, "--pp", "32", "--tg",
+                        "8", "--batch", "3", "--ctx", "20", "--reps", "2", "--json", "--dtype", "float32"], cwd=ROOT,
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    rates = json.loads(r.stdout.strip().splitlines()[-1])
+    assert set(rates) == {"pp32", "tg8"} and all(math.isfinite(x) and x > 0 for x in rates.values())
+
+
+def test_command_line_prompt_file_random_weights_cache_budget_and_stop_ids(tmp_path):
+    """``--prompt-ids FILE`` serves the file's prompts as one batch; ``--random-weights SEED`` makes
+    the model of a config.json in device memory (the same model a written folder holds);
+    ``--cache-gib`` sizes the cache; stop ids come from generation_config.json when it is there."""
+    import shutil
+    from builderforce_inference_b200 import write_model_folder
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(CONFIGS["A"]))
+    folder = str(tmp_path / "model")
+    write_model_folder(CONFIGS["A"], 31, folder, torch.float32)
+    cfg, w = P.load_folder(folder)
+    prompts = [[5, 9, 200, 31], [17], [3, 4, 5, 6, 7, 8, 9]]
+    ids_file = tmp_path / "prompts.txt"
+    ids_file.write_text("\n".join(" ".join(str(t) for t in p) for p in prompts) + "\n")
+    r = subprocess.run([sys.executable, "-m", "builderforce_inference_b200", "run", str(cfg_path), "--random-weights",
+                        "31", "--prompt-ids", str(ids_file), "--dtype", "float32", "--max-tokens", "10", "--ignore-eos",
+                        "--cache-gib", "0.001"], cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [[int(t) for t in line.split()] for line in r.stdout.strip().splitlines()]
+    assert lines == [P.greedy_generate(w, cfg, p, 10) for p in prompts]
+    # stop ids: config.json says 7; generation_config.json names the token the first prompt's
+    # free run produces at step 4, so that run now ends there
+    free = P.greedy_generate(w, cfg, prompts[0], 10, ())
+    stop = free[4]
+    with open(os.path.join(folder, "generation_config.json"), "w") as f:
+        json.dump({"eos_token_id": [stop, 300000]}, f)
+    from builderforce_inference_b200 import Model, SampleParams
+    model = Model.load(folder, dtype="float32", cache_bytes=1 << 20, cache_slots=4)
+    assert model.stop_ids == (stop, 300000, 7)
+    assert model.engine.cache_plan.max_tokens == model.engine.cache.n_pages * 64
+    assert model.engine.cache_plan.kv_bytes <= 1 << 20 < model.engine.cache_plan.kv_bytes + 256 * model.engine.cache.bytes_per_token()
+    assert model.generate(prompts[0], SampleParams(max_tokens=10)) == P.greedy_generate(w, cfg, prompts[0], 10, (stop, 7))
+    shutil.rmtree(folder)
+
+
+def test_replay_subcommand_is_trace_run(tmp_path):
+    from helpers import run_trace
+    folder = model_folder("A", torch.float32)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": [1, 2, 3, 4, 5], "want": [4]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": [6], "want": [0]}], "end": ["a"]}]
+    a = run_trace(folder, "float32", steps, 256)
+    text = "".join(json.dumps(s) + "\n" for s in steps)
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, "-m", "builderforce_inference_b200", "replay", "--model", folder, "--dtype",
+                        "float32", "--out", str(out), "--max-tokens", "256"], input=text, cwd=ROOT, capture_output=True,
+                       text=True, timeout=600)
+    assert r.returncode == 0 and r.stdout.split() == ["done", "0", "done", "1"], r.stderr[-2000:]
+    import numpy as np
+    for s in (0, 1):
+        assert torch.equal(torch.from_numpy(np.fromfile(out / f"{s}.f32", dtype="<f4")), a[s].reshape(-1))

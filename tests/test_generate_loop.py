@@ -193,3 +193,29 @@ def test_the_step_index_arrays_are_packed_in_the_layout_the_kernels_read():
         n = pack_meta(dst, tok, pos, slot_of, cu, n_tok, n_seq, seq_slots, seq_starts, 77, want)
         assert n == plain.shape[0]
         assert (dst[:n] == plain).all() and (dst[n:] == 12345).all()
+
+
+def test_pinned_staging_buffers_are_bounded_whatever_the_step_sizes():
+    """Many distinct step sizes must not grow page-locked memory: buffers are kept per power-of-two
+    capacity, four in rotation each."""
+    import numpy as np
+    from builderforce_inference_b200.engine.engine import PINNED_RING, PinnedRings
+    made = []
+
+    def make(cap):
+        made.append(cap)
+        return np.empty(cap, dtype=np.int32)
+
+    rings = PinnedRings(make)
+    sizes = list(range(1, 5000, 7))
+    for n in sizes * 3:
+        entry = rings.take(n)
+        assert len(entry[0]) >= n
+        assert len(entry[0]) == PinnedRings.capacity_for(n)
+    capacities = {PinnedRings.capacity_for(n) for n in sizes}
+    assert rings.n_buffers() == len(made) == PINNED_RING * len(capacities)
+    assert len(capacities) <= 8
+    # a ring hands its buffers out in rotation
+    first = [id(rings.take(100)[0]) for _ in range(PINNED_RING)]
+    assert len(set(first)) == PINNED_RING
+    assert [id(rings.take(100)[0]) for _ in range(PINNED_RING)] == first

@@ -181,7 +181,7 @@ def test_poisoned_cache_and_stale_rows_do_not_matter(name, dtype):
     and prompt attention kernels (64 with a window of 70, and 128); their prompts are long enough
     for the tensor-core prompt kernel (128 tokens and more in one step)."""
     long = name != "A"
-    n1, n2, k2 = (330, 300, 140) if long else (70, 45, 30)
+    n1, n2, k2, singles = (330, 300, 140, 20) if long else (70, 45, 20, 10)
     eng = load(name, dtype, max_tokens=64 * (8 if long else 4))
     folder = model_folder(name, store_dtype(dtype))
     eng.cache.poison()
@@ -192,9 +192,9 @@ def test_poisoned_cache_and_stale_rows_do_not_matter(name, dtype):
     s2 = eng.acquire()
     assert s2 == s
     got = [eng.step([S(s2, p2[:k2], list(range(k2)))]).cpu().clone()]
-    for t in p2[k2:k2 + 20]:
+    for t in p2[k2:k2 + singles]:
         got.append(eng.step([S(s2, [t], [0])]).cpu().clone())
-    rest = p2[k2 + 20:]                         # a continuation of 140 tokens over the stale rows
+    rest = p2[k2 + singles:]                    # a continuation (140 tokens for E and F) over the stale rows
     got.append(eng.step([S(s2, rest, list(range(len(rest))))]).cpu().clone())
     check(torch.cat(got), plain_logits(folder, p2), dtype, "reused slot over stale rows")
     eng.cache.check()

@@ -252,6 +252,7 @@ attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
             }
         }
     }
+    BFI_TRACE_END();
 }
 
 // Merges the ranges of every (sequence, head) in range order.
@@ -364,3 +365,5 @@ extern "C" int bfi_attention_decode_bf16(const void* q, long q_stride, void* out
     return launch_decode<128>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride, seq_slot,
                               seq_start, n_seqs, n_q, n_kv, window, scale, max_splits, part_o, part_ml, stream);
 }
+
+BFI_TRACE_EXPORT(attention_decode)

@@ -31,6 +31,9 @@ LIBRARIES: Dict[str, List[str]] = {
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
+# BFI_B200_TRACE=1 builds libraries whose kernels stamp a timeline (common.cuh); never the default
+if os.environ.get("BFI_B200_TRACE", "0") == "1":
+    NVCC_FLAGS = NVCC_FLAGS + ["-DBFI_TRACE"]
 
 
 class BuildError(RuntimeError):

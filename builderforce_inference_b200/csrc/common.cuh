@@ -36,8 +36,57 @@ int bfi_sm_count();
 // writes are visible; without the attribute the instruction returns at once.
 extern int g_bfi_pdl;
 
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;"); }
+#ifdef BFI_TRACE
+// Timeline of a step, for builds made with -DBFI_TRACE (environment variable BFI_B200_TRACE=1): the
+// first thread of every block stamps the global timer when the block starts (0), when its wait for
+// the kernel before it returns (1) and, in the kernels that say so, when it is done (2).  Records
+// are {grid id << 32 | what << 28 | linear block id, nanoseconds}; every source file has a buffer of
+// its own (BFI_TRACE_EXPORT at its end gives it a reader).
+#define BFI_TRACE_RECORDS (1 << 18)
+static __device__ unsigned long long g_bfi_trace[2 + 2 * BFI_TRACE_RECORDS];
+__device__ __forceinline__ void bfi_trace(unsigned what) {
+    if (threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) {
+        unsigned long long now, gid;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        asm volatile("mov.u64 %0, %%gridid;" : "=l"(gid));
+        const unsigned long long i = atomicAdd(&g_bfi_trace[0], 1ull);
+        if (i < BFI_TRACE_RECORDS) {
+            const unsigned long long blk = blockIdx.x + (unsigned long long)gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z);
+            g_bfi_trace[2 + 2 * i] = (gid << 32) | ((unsigned long long)what << 28) | (blk & 0xFFFFFFFull);
+            g_bfi_trace[3 + 2 * i] = now;
+        }
+    }
+}
+#define BFI_TRACE_END() bfi_trace(2)
+#define BFI_TRACE_EXPORT(name)                                                                                   \
+    extern "C" long bfi_trace_read_##name(unsigned long long* host, long cap) {                                  \
+        unsigned long long head[2] = {0, 0};                                                                     \
+        cudaDeviceSynchronize();                                                                                 \
+        cudaMemcpyFromSymbol(head, g_bfi_trace, sizeof(head));                                                   \
+        long n = (long)(head[0] < BFI_TRACE_RECORDS ? head[0] : BFI_TRACE_RECORDS);                              \
+        if (n > cap) n = cap;                                                                                    \
+        if (n > 0) cudaMemcpyFromSymbol(host, g_bfi_trace, (size_t)n * 16, 16);                                  \
+        head[0] = 0;                                                                                             \
+        cudaMemcpyToSymbol(g_bfi_trace, head, sizeof(head));                                                     \
+        return n;                                                                                                \
+    }
+#else
+#define BFI_TRACE_END()
+#define BFI_TRACE_EXPORT(name)
+#endif
+
+__device__ __forceinline__ void pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+#ifdef BFI_TRACE
+    bfi_trace(1);
+#endif
+}
+__device__ __forceinline__ void pdl_trigger() {
+#ifdef BFI_TRACE
+    bfi_trace(0);
+#endif
+    asm volatile("griddepcontrol.launch_dependents;");
+}
 
 template <typename... KArgs, typename... Args>
 static inline cudaError_t bfi_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,

@@ -537,3 +537,5 @@ extern "C" int bfi_residual_add(float* x, const void* y, int y_dtype, long n, cu
         bfi_launch(residual_add_kernel<bf16>, dim3(blocks), dim3(threads), 0, stream, x, (const bf16*)y, n);
     return bfi_check_launch("residual_add");
 }
+
+BFI_TRACE_EXPORT(elementwise)

@@ -232,3 +232,5 @@ extern "C" int bfi_gemm_simt(const void* A, int a_dtype, long lda, const void* W
     }
     return 0;
 }
+
+BFI_TRACE_EXPORT(gemm_simt)

@@ -289,6 +289,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         tc_fence_after();
         tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
+    BFI_TRACE_END();
 }
 
 // ------------------------------------------------------------------------------------------
@@ -834,3 +835,5 @@ extern "C" int bfi_gemm_tcgen05_bf16_wait_probe(const void* A, long lda, const v
     return gemm_tcgen05_launch(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, epilogue, status, stream,
                                TcWaits{spin_limit, hold_producer ? 1 : 0});
 }
+
+BFI_TRACE_EXPORT(gemm_tcgen05)

@@ -614,3 +614,5 @@ extern "C" int bfi_argmax_rows(const float* logits, long stride, int n_rows, int
     bfi_launch(argmax_rows_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, stride, vocab, out);
     return bfi_check_launch("argmax_rows");
 }
+
+BFI_TRACE_EXPORT(sampling)

@@ -65,6 +65,9 @@ class StepContext:
     host_seq_start: Optional[List[int]] = None
     host_seq_tokens: Optional[List[int]] = None
     capturing: bool = False
+    # single-token steps: a power of two at or above the most cache pages any sequence of the step
+    # holds (0: unknown).  Kernels may size their work split by it; no result depends on it.
+    pages_bucket: int = 0
     extras: dict = field(default_factory=dict)
 
     def rows(self, tag: str, n_cols: int, dtype: Optional[torch.dtype] = None,

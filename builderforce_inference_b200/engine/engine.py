@@ -138,8 +138,23 @@ def _require_gpu(device: torch.device) -> None:
         raise RuntimeError("this engine runs on an NVIDIA GPU only (sm_100a kernels); no CUDA device is available")
 
 
-class _DecodeGraph:
-    """A captured single-token step for one padded batch size."""
+PAGE_BUCKETS_STEP = 4     # page-count buckets of single-token steps: 1, 4, 16, 64, ... pages per sequence
+
+
+def pages_bucket(most_pages: int, limit: int) -> int:
+    """The smallest bucket (a power of ``PAGE_BUCKETS_STEP``) that holds ``most_pages``, capped by
+    the bucket that holds ``limit`` (the most pages a sequence can have)."""
+    b = 1
+    while b < most_pages and b < limit:
+        b *= PAGE_BUCKETS_STEP
+    return b
+
+
+class _DecodeGraphs:
+    """The captured single-token steps of one padded batch size: one graph per page-count bucket
+    (kernels cut their work by the most pages a sequence of the step holds), all over the same
+    index arrays and logits.  Every bucket is captured when the batch size is first seen, so no
+    capture falls into the middle of a generation."""
 
     def __init__(self, engine: "Engine", batch: int):
         self.batch = batch
@@ -147,22 +162,34 @@ class _DecodeGraph:
         self.meta = torch.zeros(engine._meta_len(batch, batch, 0), dtype=torch.int32, device=dev)
         self.logits = torch.empty((batch, engine.spec.vocab_size), dtype=torch.float32, device=dev)
         self.rows = torch.arange(batch, dtype=torch.int32, device=dev)
-        self.stamp = engine._stamp()
         # every row starts as padding (slot -1), so the runs below touch no sequence's cache
         engine._fill_meta(self.meta, [], [], [], [0], batch, batch)
-        ctx = engine._context_from_meta(self.meta, batch, batch, 1, None)
-        # eager run first: loads kernels, sizes the workspace, sets launch attributes
-        engine._forward(ctx, self.rows, self.logits)
-        torch.cuda.synchronize(dev)
-        if self.stamp != engine._stamp():
-            self.stamp = engine._stamp()
+        self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self.n_kernels: Dict[int, int] = {}
+        limit = engine.cache.n_blocks
+        buckets, b = [], 1
+        while True:
+            buckets.append(b)
+            if b >= limit:
+                break
+            b *= PAGE_BUCKETS_STEP
+        # eager runs first: they load kernels, size the workspace and set launch attributes
+        for b in buckets:
             ctx = engine._context_from_meta(self.meta, batch, batch, 1, None)
-        ctx.capturing = True
-        self.graph = torch.cuda.CUDAGraph()
-        before = total_calls()
-        with torch.cuda.graph(self.graph):
+            ctx.pages_bucket = b
             engine._forward(ctx, self.rows, self.logits)
-        self.n_kernels = total_calls() - before      # launches one replay stands for
+        torch.cuda.synchronize(dev)
+        self.stamp = engine._stamp()
+        for b in buckets:
+            ctx = engine._context_from_meta(self.meta, batch, batch, 1, None)
+            ctx.pages_bucket = b
+            ctx.capturing = True
+            graph = torch.cuda.CUDAGraph()
+            before = total_calls()
+            with torch.cuda.graph(graph):
+                engine._forward(ctx, self.rows, self.logits)
+            self.graphs[b] = graph
+            self.n_kernels[b] = total_calls() - before      # launches one replay stands for
 
 
 class Engine:
@@ -200,7 +227,7 @@ class Engine:
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.prefill_chunk_tokens = max(PAGE_TOKENS, int(prefill_chunk_tokens))
         self.use_graphs = bool(use_graphs) and self.decoder.graph_safe()
-        self._graphs: Dict[int, _DecodeGraph] = {}
+        self._graphs: Dict[int, _DecodeGraphs] = {}
         self._pinned = PinnedRings()
         self.last_h2d_bytes = 0        # bytes of index arrays the last step copied to the device
         self.graph_kernel_launches = 0  # kernels launched through graph replays so far
@@ -321,6 +348,9 @@ class Engine:
         b = len(seqs)
         tokens = [int(s.tokens[0]) for s in seqs]
         want_rows = [i for i, s in enumerate(seqs) if len(s.want) > 0]
+        # the most pages a sequence of this step holds, rounded up to a bucket: kernels cut their
+        # work by it, so a step over short sequences does not launch for the longest possible one
+        bucket = pages_bucket(max((st + PAGE_TOKENS) // PAGE_TOKENS for st in starts), self.cache.n_blocks)
         if self.use_graphs:
             padded = 1
             while padded < b:
@@ -329,16 +359,17 @@ class Engine:
                 padded = ((b + 15) // 16) * 16
             g = self._graphs.get(padded)
             if g is None or g.stamp != self._stamp():
-                g = _DecodeGraph(self, padded)
+                g = _DecodeGraphs(self, padded)
                 self._graphs[padded] = g
             self._fill_meta(g.meta, tokens, starts, slots, list(range(b + 1)), padded, padded)
-            g.graph.replay()
-            self.graph_kernel_launches += g.n_kernels
+            g.graphs[bucket].replay()
+            self.graph_kernel_launches += g.n_kernels[bucket]
             logits = g.logits
         else:
             meta = self._meta_buffer(b, b, 0)
             self._fill_meta(meta, tokens, starts, slots, list(range(b + 1)), b, b)
             ctx = self._context_from_meta(meta, b, b, 1, (slots, starts, [1] * b))
+            ctx.pages_bucket = bucket
             logits = self.workspace.rows("logits", b, self.spec.vocab_size, torch.float32)
             rows = torch.arange(b, dtype=torch.int32, device=self.device)
             self._forward(ctx, rows, logits)

@@ -151,13 +151,19 @@ def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
     return False
 
 
+DECODE_PAGES_PER_BLOCK = 24     # a block's range should not be much longer than this many pages
+
+
 def decode_splits(n_seqs: int, n_kv: int, group: int, max_pages: int, n_sm: int) -> int:
     """Into how many page ranges every (sequence, kv head) is cut: enough blocks to fill the GPU
-    once (two to three blocks are resident on an SM), never more than a sequence can have pages.
-    Depends only on sizes that are fixed when a step is captured."""
+    once (two to three blocks are resident on an SM), and enough that no block walks a very long
+    range alone (with many sequences one range each fills the GPU, but 64 pages in a row make a
+    long tail); never more than a sequence can have pages.  Depends only on sizes that are fixed
+    when a step is captured."""
     blocks = n_seqs * n_kv * ((group + 15) // 16)
-    want = (n_sm * 5 // 2 + blocks - 1) // blocks
-    return max(1, min(want, max_pages, 32))
+    fill = (n_sm * 5 // 2 + blocks - 1) // blocks
+    length = (max_pages + DECODE_PAGES_PER_BLOCK - 1) // DECODE_PAGES_PER_BLOCK
+    return max(1, min(max(fill, length), max_pages, 32))
 
 
 def attention_decode_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float) -> bool:
@@ -165,6 +171,11 @@ def attention_decode_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads
     if d not in (64, 128) or qkv.dtype != torch.bfloat16 or kv.k.dtype != torch.bfloat16:
         return False
     max_pages = kv.block_table.shape[1]
+    bucket = getattr(ctx, "pages_bucket", 0)
+    if bucket:
+        max_pages = min(max_pages, bucket)           # what the step's sequences hold now, rounded up
+    if kv.window:
+        max_pages = min(max_pages, (kv.window + 62) // 64 + 1)
     group = n_heads // kv.n_kv_heads
     max_splits = decode_splits(ctx.n_seqs, kv.n_kv_heads, group, max_pages, sm_count(qkv.device))
     part_o = part_ml = None

@@ -219,3 +219,10 @@ def test_pinned_staging_buffers_are_bounded_whatever_the_step_sizes():
     first = [id(rings.take(100)[0]) for _ in range(PINNED_RING)]
     assert len(set(first)) == PINNED_RING
     assert [id(rings.take(100)[0]) for _ in range(PINNED_RING)] == first
+
+
+def test_page_buckets_of_single_token_steps():
+    from builderforce_inference_b200.engine.engine import pages_bucket
+    assert [pages_bucket(n, 64) for n in (1, 2, 4, 5, 16, 17, 64)] == [1, 4, 4, 16, 16, 64, 64]
+    assert pages_bucket(33, 40) == 64 and pages_bucket(40, 40) == 64       # the last bucket holds the limit
+    assert pages_bucket(3, 2) == 4 and pages_bucket(1, 1) == 1

@@ -386,3 +386,150 @@ def test_toy_architecture_with_routing_another_position_encoding_and_another_nor
         undo()
     from builderforce_inference_b200 import registered_architectures
     assert registered_architectures() == ["Qwen3ForCausalLM", "qwen3"]
+
+
+# ------------------------------------------------------------------------------------------------
+# A third unknown model: a mixer that keeps keys and values AND a fixed-size state (attention
+# whose output is joined by a running sum of its input).  Its cache need is a pair; the run's
+# cache then carries both entries.  The layer runs twice, so there are two such pairs.
+# ------------------------------------------------------------------------------------------------
+H_WIDTH, H_HEADS, H_KV, H_D, H_INNER, H_VOCAB, H_EPS, H_THETA, H_DECAY = 56, 3, 3, 32, 72, 83, 1e-6, 3e3, 0.6
+HYBRID_CONFIG = {"architectures": ["ToyHybridLM"], "model_type": "toy_hybrid", "vocab_size": H_VOCAB,
+                 "max_position_embeddings": 192}
+
+
+def register_hybrid():
+    from builderforce_inference_b200 import Architecture, register_architecture, unregister_architecture
+    from builderforce_inference_b200.parts import KVNeed, LayerSpec, MIXERS, ModelSpec, ParamSpec, PartSpec, RunSpec, StateNeed
+    from builderforce_inference_b200.parts.attention import Attention
+
+    class AttentionWithRunningSum(Attention):
+        """out = attention(h) + s_t @ mix^T with s_t = decay * s_{t-1} + h_t: keys and values in
+        pages, s in a per-sequence state of ``width`` floats."""
+        graph_safe = False
+
+        def __init__(self, decay, **kw):
+            super().__init__(**kw)
+            self.decay = decay
+
+        def param_specs(self):
+            specs = dict(super().param_specs())
+            specs["mix"] = ParamSpec((self.width, self.width))
+            return specs
+
+        def load(self, tensors, runtime):
+            super().load(tensors, runtime)
+            self.mix = tensors["mix"].float()
+
+        def cache_need(self):
+            return (KVNeed(self.n_kv_heads, self.head_dim, self.window), StateNeed((self.width,), "float32"))
+
+        def forward(self, ctx, h, residual, run):
+            assert isinstance(run.entries[1], torch.Tensor) and run.entries[0] is run.kv and run.entries[1] is run.state
+            super().forward(ctx, h, residual, run)
+            row = 0
+            for slot, n in zip(ctx.host_seq_slot, ctx.host_seq_tokens):
+                s = run.state[slot]
+                for t in range(n):
+                    s.mul_(self.decay).add_(h[row + t].float())
+                    residual[row + t] += s @ self.mix.t()
+                row += n
+
+    MIXERS.register("attention_running_sum", AttentionWithRunningSum)
+
+    def describe(config):
+        norm = PartSpec("rms", {"width": H_WIDTH, "eps": H_EPS})
+        ffn = PartSpec("gated_mlp", {"width": H_WIDTH, "inner": H_INNER})
+        rot = PartSpec("rotary", {"theta": H_THETA, "rot_dim": H_D})
+        att = {"width": H_WIDTH, "n_heads": H_HEADS, "n_kv_heads": H_KV, "head_dim": H_D, "position": rot}
+
+        def layer(i, mixer, extra):
+            names = {"norm1.weight": f"b{i}.n1", "norm2.weight": f"b{i}.n2", "ffn.gate_proj": f"b{i}.gate",
+                     "ffn.up_proj": f"b{i}.up", "ffn.down_proj": f"b{i}.down"}
+            names.update({f"mixer.{k}": f"b{i}.{k}" for k in ["q_proj", "k_proj", "v_proj", "o_proj"] + extra})
+            return LayerSpec(PartSpec("prenorm", {"norm1": norm, "mixer": mixer, "norm2": norm, "ffn": ffn}), names)
+
+        layers = (layer(0, PartSpec("attention_running_sum", dict(att, decay=H_DECAY)), ["mix"]),
+                  layer(1, PartSpec("attention", att), []))
+        return ModelSpec(vocab_size=config["vocab_size"], width=H_WIDTH, embedding_name="emb", layers=layers,
+                         schedule=(RunSpec(0), RunSpec(1), RunSpec(0)), final_norm=norm,
+                         final_norm_names={"weight": "out_norm"}, head_name=None,
+                         max_positions=config["max_position_embeddings"])
+
+    register_architecture(("toy_hybrid", "ToyHybridLM"), Architecture("toy_hybrid", dict, describe))
+
+    def undo():
+        unregister_architecture("toy_hybrid", "ToyHybridLM")
+        MIXERS.unregister("attention_running_sum")
+    return undo
+
+
+def plain_hybrid(w, tokens):
+    t = len(tokens)
+    pos = list(range(t))
+    x = P.embedding(w["emb"], tokens)
+
+    def block(x, i, running_sum):
+        h = P.rms_norm(x, w[f"b{i}.n1"], H_EPS)
+        q = P.rope_neox(P.linear(w[f"b{i}.q_proj"], h).reshape(t, H_HEADS, H_D), pos, H_THETA)
+        k = P.rope_neox(P.linear(w[f"b{i}.k_proj"], h).reshape(t, H_KV, H_D), pos, H_THETA)
+        v = P.linear(w[f"b{i}.v_proj"], h).reshape(t, H_KV, H_D)
+        x = x + P.linear(w[f"b{i}.o_proj"], P.attention(q, k, v).reshape(t, H_HEADS * H_D))
+        if running_sum:
+            s = torch.zeros(H_WIDTH)
+            ys = []
+            for r in range(t):
+                s = H_DECAY * s + h[r]
+                ys.append(s @ w[f"b{i}.mix"].t())
+            x = x + torch.stack(ys)
+        h = P.rms_norm(x, w[f"b{i}.n2"], H_EPS)
+        return x + P.linear(w[f"b{i}.down"], P.swiglu(P.linear(w[f"b{i}.gate"], h), P.linear(w[f"b{i}.up"], h)))
+
+    x = block(block(block(x, 0, True), 1, False), 0, True)
+    return P.linear(w["emb"], P.rms_norm(x, w["out_norm"], H_EPS))
+
+
+def test_toy_mixer_with_keys_and_values_and_a_state_of_its_own():
+    from builderforce_inference_b200 import write_model_folder
+    from builderforce_inference_b200.engine.engine import Engine, SequenceStep as S, StepError
+    undo = register_hybrid()
+    try:
+        folder = tempfile.mkdtemp(prefix="bfi_toy_hybrid_")
+        write_model_folder(HYBRID_CONFIG, 8, folder, torch.float32)
+        w = {k: v.float() for k, v in P.read_safetensors(os.path.join(folder, "model.safetensors")).items()}
+        eng = Engine.load(folder, dtype="float32", max_tokens=1024)
+        # the three runs' keys and values share one group; the two hybrid runs' states another
+        assert [g.keys for g in eng.cache.kv_groups] == [[(0, 0), (1, 0), (2, 0)]]
+        assert [g.keys for g in eng.cache.state_groups] == [[(0, 1), (2, 1)]]
+        assert eng.cache.state_bytes_per_slot() == 2 * H_WIDTH * 4
+        g = torch.Generator().manual_seed(4)
+        prompts = [torch.randint(0, H_VOCAB, (n,), generator=g).tolist() for n in (90, 13, 41)]
+        refs = [plain_hybrid(w, p) for p in prompts]
+        for p, r in zip(prompts, refs):
+            s = eng.acquire()
+            assert rel_err(eng.step([S(s, p, list(range(len(p))))]).cpu(), r) < 1e-4
+            eng.release(s)
+        slots = [eng.acquire() for _ in prompts]
+        pre = [70, 4, 30]
+        lg = eng.step([S(s, p[:k], [k - 1]) for s, p, k in zip(slots, prompts, pre)]).cpu().clone()
+        for i, k in enumerate(pre):
+            assert rel_err(lg[i:i + 1], refs[i][k - 1:k]) < 1e-4
+        pos = list(pre)
+        live = [0, 1, 2]
+        while live:
+            lg = eng.step([S(slots[i], [prompts[i][pos[i]]], [0]) for i in live]).cpu().clone()
+            for j, i in enumerate(live):
+                assert rel_err(lg[j:j + 1], refs[i][pos[i]:pos[i] + 1]) < 1e-4, (i, pos[i])
+                pos[i] += 1
+            for i in list(live):
+                if pos[i] == len(prompts[i]):
+                    if i == 0:
+                        with pytest.raises(StepError, match="rewind unsupported.*fixed size"):
+                            eng.rewind(slots[i], 5)          # a state cannot be wound back
+                    eng.release(slots[i])
+                    live.remove(i)
+        eng.cache.check()
+    finally:
+        undo()
+    from builderforce_inference_b200 import registered_architectures
+    assert registered_architectures() == ["Qwen3ForCausalLM", "qwen3"]

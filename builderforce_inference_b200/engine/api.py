@@ -25,10 +25,23 @@ class GreedyTrace:
     last_logits: torch.Tensor
 
 
+@dataclass
+class _SampleTicket:
+    """Ids the sampler left on the device, on their way to a pinned host buffer."""
+
+    ids: torch.Tensor             # int32 [n] on the device
+    host: torch.Tensor            # pinned int32, at least n
+    n: int
+    arrived: torch.cuda.Event
+
+
 class EngineStepper:
     """What the generation loop needs from an engine: slots, steps and sampling, with host token
     ids in and out.  Every step copies its inputs from pinned host memory and reads the chosen
-    ids back into pinned host memory."""
+    ids back into pinned host memory.  ``pipelined``: a single-token step can take its ids straight
+    from the sampler's device buffer, so the loop may launch it before the host has read them."""
+
+    pipelined = True
 
     def __init__(self, engine: Engine):
         self.engine = engine
@@ -37,6 +50,8 @@ class EngineStepper:
         self.n_pages = engine.cache.n_pages
         self.sampler = Sampler(engine.device, engine.spec.vocab_size)
         self._host_ids = torch.empty(1024, dtype=torch.int32, pin_memory=True)
+        self._ticket_bufs = [torch.empty(1024, dtype=torch.int32, pin_memory=True) for _ in range(3)]
+        self._ticket_turn = 0
         self.last_logits: Optional[torch.Tensor] = None
         self.on_tokens = None          # called with the number of ids after each read-back
         self.h2d_bytes = 0
@@ -71,6 +86,38 @@ class EngineStepper:
         if self.on_tokens is not None:
             self.on_tokens(n)
         return host.tolist()
+
+
+    # ---- one step ahead of the host ----------------------------------------------------
+    def sample_start(self, handle, params: SampleParams, requests, steps) -> _SampleTicket:
+        ids = self.sampler.sample(handle, params, requests, steps, None)
+        n = ids.numel()
+        i = self._ticket_turn
+        self._ticket_turn = (i + 1) % len(self._ticket_bufs)
+        if self._ticket_bufs[i].numel() < n:
+            self._ticket_bufs[i] = torch.empty(2 * n, dtype=torch.int32, pin_memory=True)
+        host = self._ticket_bufs[i]
+        host[:n].copy_(ids, non_blocking=True)
+        arrived = torch.cuda.Event()
+        arrived.record(torch.cuda.current_stream(self.engine.device))
+        return _SampleTicket(ids, host, n, arrived)
+
+    def sample_wait(self, ticket: _SampleTicket) -> List[int]:
+        ticket.arrived.synchronize()
+        self.d2h_bytes = ticket.n * 4
+        if self.on_tokens is not None:
+            self.on_tokens(ticket.n)
+        return ticket.host[:ticket.n].tolist()
+
+    def decode_sampled(self, slots: Sequence[int], ticket: _SampleTicket, rows: Sequence[int]):
+        ids = ticket.ids
+        if list(rows) != list(range(ticket.n)):
+            # some sequences of the ticket ended: the others' ids, gathered on the device
+            index = torch.tensor(list(rows), dtype=torch.long, device=ids.device)
+            ids = ids.index_select(0, index)
+        self.last_logits = self.engine.step_sampled(slots, ids, check=False)
+        self.h2d_bytes = self.engine.last_h2d_bytes
+        return self.last_logits
 
 
 class Model:

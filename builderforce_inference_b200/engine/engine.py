@@ -314,9 +314,32 @@ class Engine:
         starts = [self.cache.length(s) for s in slots]
 
         if all(c == 1 for c in counts):
-            out = self._decode_step(seqs, slots, starts)
+            out = self._decode_step([int(s.tokens[0]) for s in seqs], [i for i, s in enumerate(seqs) if len(s.want) > 0],
+                                    slots, starts)
         else:
             out = self._prefill_step(seqs, slots, starts, counts)
+        self.cache.end_step(slots, counts)
+        if check:
+            self.check_status()
+        return out
+
+    def step_sampled(self, slots: Sequence[int], token_ids: torch.Tensor, check: bool = True) -> torch.Tensor:
+        """One token for each of ``slots``, the ids taken from ``token_ids`` (int32 on the device,
+        for instance where the sampler left them) without a trip through the host; logits for every
+        sequence.  The ids must be valid: nothing but the embedding's own check sees them."""
+        slots = [int(s) for s in slots]
+        if not slots:
+            raise StepError("a step needs at least one sequence")
+        if token_ids.dtype != torch.int32 or not token_ids.is_cuda or token_ids.numel() != len(slots) \
+                or not token_ids.is_contiguous():
+            raise StepError(f"step_sampled wants {len(slots)} contiguous int32 ids on the device")
+        counts = [1] * len(slots)
+        try:
+            self.cache.begin_step(slots, counts)
+        except CacheError as e:
+            raise StepError(str(e)) from e
+        starts = [self.cache.length(s) for s in slots]
+        out = self._decode_step([0] * len(slots), list(range(len(slots))), slots, starts, token_ids)
         self.cache.end_step(slots, counts)
         if check:
             self.check_status()
@@ -344,10 +367,10 @@ class Engine:
             raise StepError("device-side check failed: " + "; ".join(what))
 
     # ---- single-token steps ----------------------------------------------------------
-    def _decode_step(self, seqs, slots, starts) -> torch.Tensor:
-        b = len(seqs)
-        tokens = [int(s.tokens[0]) for s in seqs]
-        want_rows = [i for i, s in enumerate(seqs) if len(s.want) > 0]
+    def _decode_step(self, tokens, want_rows, slots, starts, device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``device_tokens`` (int32 on the device, one per sequence) replace ``tokens`` after the
+        step's index arrays have been copied: the ids then never pass through the host."""
+        b = len(slots)
         # the most pages a sequence of this step holds, rounded up to a bucket: kernels cut their
         # work by it, so a step over short sequences does not launch for the longest possible one
         bucket = pages_bucket(max((st + PAGE_TOKENS) // PAGE_TOKENS for st in starts), self.cache.n_blocks)
@@ -362,12 +385,16 @@ class Engine:
                 g = _DecodeGraphs(self, padded)
                 self._graphs[padded] = g
             self._fill_meta(g.meta, tokens, starts, slots, list(range(b + 1)), padded, padded)
+            if device_tokens is not None:
+                g.meta[:b].copy_(device_tokens, non_blocking=True)
             g.graphs[bucket].replay()
             self.graph_kernel_launches += g.n_kernels[bucket]
             logits = g.logits
         else:
             meta = self._meta_buffer(b, b, 0)
             self._fill_meta(meta, tokens, starts, slots, list(range(b + 1)), b, b)
+            if device_tokens is not None:
+                meta[:b].copy_(device_tokens, non_blocking=True)
             ctx = self._context_from_meta(meta, b, b, 1, (slots, starts, [1] * b))
             ctx.pages_bucket = bucket
             logits = self.workspace.rows("logits", b, self.spec.vocab_size, torch.float32)

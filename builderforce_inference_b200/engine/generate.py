@@ -14,6 +14,14 @@ exhausts the budget is not forwarded, since nothing would read its logits.
 
 The loop talks to the model only through ``acquire / release / step / sample``, so its decisions
 are tested on the CPU against a toy stepper.
+
+A stepper that can feed a step with the ids the sampler left on the device (``pipelined``) is driven
+one step ahead: step k+1 is launched before the host has read token k, so the host's work (the
+copy back, the stop test, packing the next step) runs beside the GPU instead of between its
+steps.  What the host then learns about token k (a stop token) can only end a sequence, and a
+sequence that ended takes at most one step too many, whose token is dropped; the results are
+those of the plain loop, token for token.  Penalties need the host's history of every sequence
+before sampling, so they keep the plain loop.
 """
 from __future__ import annotations
 
@@ -47,6 +55,7 @@ class _Live:
     budget: int
     history: List[int]
     generated: List[int] = field(default_factory=list)
+    alive: bool = True
 
 
 def token_budget(prompt_len: int, max_tokens: int, max_seq_len: int) -> int:
@@ -78,6 +87,63 @@ def plan_batches(prompt_lens: Sequence[int], budgets: Sequence[int], max_batch: 
     if cur:
         batches.append(cur)
     return batches
+
+
+def _run_pipelined(stepper, live: List[_Live], prompts, params: SampleParams, stop, results, on_step) -> int:
+    """One batch, one step ahead of the host.  The stepper provides, beside the plain interface:
+
+    ``sample_start(handle, params, requests, steps) -> ticket``: launch the sampling and the copy of
+    the ids to the host, without waiting;
+    ``sample_wait(ticket) -> list[int]``: the ids, once they have arrived;
+    ``decode_sampled(slots, ticket, rows) -> handle``: one step in which sequence ``i`` takes the id
+    the ticket holds at ``rows[i]``, fed on the device.
+
+    Returns the number of shared single-token steps whose tokens were used."""
+    handle = stepper.prefill([s.slot for s in live], [prompts[s.request] for s in live])
+    ticket = stepper.sample_start(handle, params, [s.request for s in live], [0] * len(live))
+    members = list(live)              # the sequences whose ids the ticket holds, row by row
+    launched = shared = 0
+    first = True
+    while True:
+        # the step after the ids in flight, for everyone those ids cannot be the last of
+        go = [(i, s) for i, s in enumerate(members) if s.alive and len(s.generated) + 1 < s.budget]
+        nxt = None
+        if go and launched < MAX_SHARED_STEPS - 1:
+            handle = stepper.decode_sampled([s.slot for _, s in go], ticket, [i for i, _ in go])
+            launched += 1
+            nxt = stepper.sample_start(handle, params, [s.request for _, s in go],
+                                       [len(s.generated) + 1 for _, s in go])
+        picked = stepper.sample_wait(ticket)
+        used = 0
+        for s, tok in zip(members, picked):
+            if not s.alive:
+                continue                       # ended a step ago: this id belongs to nobody
+            used += 1
+            tok = int(tok)
+            if tok in stop:
+                results[s.request] = Generated(s.generated, "stop")
+            else:
+                s.generated.append(tok)
+                s.history.append(tok)
+                if len(s.generated) < s.budget:
+                    continue
+                results[s.request] = Generated(s.generated, "length")
+            s.alive = False
+            stepper.release(s.slot)
+        if not first and used:
+            shared += 1
+            if on_step is not None:
+                on_step(shared, used)
+        first = False
+        if nxt is None:
+            break
+        members, ticket = [s for _, s in go], nxt
+    for s in live:                             # the cap on shared steps was reached
+        if s.alive:
+            results[s.request] = Generated(s.generated, "length")
+            s.alive = False
+            stepper.release(s.slot)
+    return shared
 
 
 def generate_batch(stepper, prompts: Sequence[Sequence[int]], params: SampleParams,
@@ -112,6 +178,9 @@ def generate_batch(stepper, prompts: Sequence[Sequence[int]], params: SamplePara
         if not live:
             continue
         try:
+            if getattr(stepper, "pipelined", False) and not params.has_penalties:
+                report.shared_steps += _run_pipelined(stepper, live, prompts, params, stop, results, on_step)
+                continue
             handle = stepper.prefill([s.slot for s in live], [prompts[s.request] for s in live])
             shared = 0
             while live:
@@ -123,12 +192,14 @@ def generate_batch(stepper, prompts: Sequence[Sequence[int]], params: SamplePara
                     tok = int(tok)
                     if tok in stop:
                         results[s.request] = Generated(s.generated, "stop")
+                        s.alive = False
                         stepper.release(s.slot)
                         continue
                     s.generated.append(tok)
                     s.history.append(tok)
                     if len(s.generated) >= s.budget:
                         results[s.request] = Generated(s.generated, "length")
+                        s.alive = False
                         stepper.release(s.slot)
                         continue
                     still.append(s)
@@ -139,6 +210,7 @@ def generate_batch(stepper, prompts: Sequence[Sequence[int]], params: SamplePara
                 if shared >= MAX_SHARED_STEPS:
                     for s in live:
                         results[s.request] = Generated(s.generated, "length")
+                        s.alive = False
                         stepper.release(s.slot)
                     live = []
                     break
@@ -148,6 +220,8 @@ def generate_batch(stepper, prompts: Sequence[Sequence[int]], params: SamplePara
             report.shared_steps += shared
         except BaseException:
             for s in live:
+                if not s.alive:
+                    continue
                 try:
                     stepper.release(s.slot)
                 except Exception:

@@ -445,3 +445,27 @@ def test_the_benchmark_lengths_against_plain(dtype):
         for sl in slots:
             eng.release(sl)
     eng.cache.check()
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_a_step_fed_from_device_ids_equals_the_same_step_from_host_ids(graphs):
+    name, dtype = "B", "float32"
+    folder = model_folder(name, store_dtype(dtype))
+    prompts = random_prompts(CONFIGS[name]["vocab_size"], [20, 3, 41], seed=33)
+    nxt = [7, 300, 123]
+    outs = []
+    for fed_on_device in (False, True):
+        eng = load(name, dtype, use_graphs=graphs)
+        slots = [eng.acquire() for _ in prompts]
+        eng.step([S(s, p, []) for s, p in zip(slots, prompts)])
+        if fed_on_device:
+            ids = torch.tensor(nxt, dtype=torch.int32, device="cuda:0")
+            outs.append(eng.step_sampled(slots, ids).cpu().clone())
+            outs.append(eng.step_sampled(slots[:2], ids[1:].contiguous()).cpu().clone())
+        else:
+            outs.append(eng.step([S(s, [t], [0]) for s, t in zip(slots, nxt)]).cpu().clone())
+            outs.append(eng.step([S(s, [t], [0]) for s, t in zip(slots[:2], nxt[1:])]).cpu().clone())
+        assert [eng.length(s) for s in slots] == [22, 5, 42]
+    assert torch.equal(outs[0], outs[2]) and torch.equal(outs[1], outs[3])
+    ref = plain_logits(folder, prompts[0] + [nxt[0], nxt[1]])
+    assert rel_err(outs[3][0:1], ref[-1:]) < tol(dtype)

@@ -226,3 +226,56 @@ def test_page_buckets_of_single_token_steps():
     assert [pages_bucket(n, 64) for n in (1, 2, 4, 5, 16, 17, 64)] == [1, 4, 4, 16, 16, 64, 64]
     assert pages_bucket(33, 40) == 64 and pages_bucket(40, 40) == 64       # the last bucket holds the limit
     assert pages_bucket(3, 2) == 4 and pages_bucket(1, 1) == 1
+
+
+class AheadToyStepper(ToyStepper):
+    """The toy stepper with the one-step-ahead interface: a ticket is the list of ids "on the
+    device"; the loop may read it only through ``sample_wait``."""
+
+    pipelined = True
+
+    def __init__(self, *a, **k):
+        super().__init__(*a, **k)
+        self.waited = 0
+
+    def sample_start(self, handle, params, requests, steps):
+        return {"ids": [next_token(self.hist[s]) for s in handle], "read": False}
+
+    def sample_wait(self, ticket):
+        assert not ticket["read"], "a ticket is read once"
+        ticket["read"] = True
+        self.waited += 1
+        return list(ticket["ids"])
+
+    def decode_sampled(self, slots, ticket, rows):
+        assert not ticket["read"], "the next step must be launched before the host reads the ids"
+        return self.decode(slots, [ticket["ids"][r] for r in rows])
+
+
+@pytest.mark.parametrize("max_tokens,n_stop", [(8, 0), (12, 2), (1, 0), (2, 1), (30, 3)])
+def test_one_step_ahead_gives_the_plain_loops_results(max_tokens, n_stop):
+    """The loop that launches step k+1 before it has read token k returns what the plain loop
+    returns: same tokens, finish reasons, count of shared steps; every slot is given back; a
+    sequence that met its stop token takes at most one step too many."""
+    prompts = [[3, 1, 4], [1, 5, 9, 2], [6, 5], [3, 5, 8, 9, 7, 9], [2]]
+    free_run = [expected(p, 30)[0] for p in prompts]
+    stop = {free_run[i][min(i + 1, max_tokens - 1)] for i in range(n_stop)}
+    plain, ahead = ToyStepper(max_seq_len=64), AheadToyStepper(max_seq_len=64)
+    a = generate_batch(plain, prompts, SampleParams(max_tokens=max_tokens), stop_ids=stop, max_batch=3)
+    b = generate_batch(ahead, prompts, SampleParams(max_tokens=max_tokens), stop_ids=stop, max_batch=3)
+    assert [(r.tokens, r.finish_reason) for r in b.results] == [(r.tokens, r.finish_reason) for r in a.results]
+    for p, r in zip(prompts, b.results):
+        assert (r.tokens, r.finish_reason) == expected(p, max_tokens, stop)
+    assert (b.shared_steps, b.generated_tokens, b.batches) == (a.shared_steps, a.generated_tokens, a.batches)
+    assert ahead.hist == {} and sorted(ahead.free) == [0, 1, 2, 3]
+    n_plain = sum(1 for k, _ in plain.log if k == "decode")
+    n_ahead = sum(1 for k, _ in ahead.log if k == "decode")
+    assert n_plain <= n_ahead <= n_plain + (2 if n_stop else 0)      # at most one extra step per batch
+    if not n_stop:
+        assert [n for _, n in ahead.log] == [n for _, n in plain.log]
+
+
+def test_penalties_keep_the_plain_loop():
+    st = AheadToyStepper()
+    generate_batch(st, [[1, 2, 3]], SampleParams(max_tokens=4, repeat_penalty=1.2), max_batch=1)
+    assert st.waited == 0 and len(st.log) == 4

@@ -428,8 +428,89 @@ def kernel_run(a) -> int:
     return 0
 
 
+TRACE_UNITS = [("core", "elementwise"), ("core", "sampling"), ("core", "gemm_simt"), ("fast", "gemm_tcgen05"),
+               ("fast", "attention_decode")]
+
+
+def timeline_run(a) -> int:
+    """``--timeline``: one decode step's kernels on the GPU's own clock.  The libraries are built
+    with time stamps in the kernels (BFI_B200_TRACE=1, set below before the package loads): the first
+    thread of every block records when it starts, when its wait for the kernel before it returns and
+    (products and attention) when it ends.  Prints, for the kernels of ``--timeline-layer``, the
+    first and last of each stamp in microseconds from the step's start: where the step's time goes
+    between the kernels, which no serialised profile shows."""
+    import ctypes
+
+    import numpy as np
+    import torch
+    from builderforce_inference_b200 import Model
+    from builderforce_inference_b200.engine.engine import SequenceStep
+    from builderforce_inference_b200.kernels.library import library
+    layers = a.layers or 12
+    cfg = dict(SHAPES[a.shape_name], num_hidden_layers=layers)
+    model = Model.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=a.batch * CONTEXT, max_seq_len=CONTEXT, max_batch=a.batch)
+    eng = model.engine
+    g = torch.Generator().manual_seed(2)
+    lens = torch.randint(128, 2049, (a.batch,), generator=g).tolist()
+    slots = [eng.acquire() for _ in lens]
+    eng.step([SequenceStep(s, torch.randint(0, 1000, (n,), generator=g).tolist(), ()) for s, n in zip(slots, lens)], check=False)
+
+    def one():
+        eng.step([SequenceStep(s, (5,), (0,)) for s in slots], check=False)
+
+    for _ in range(6):
+        one()
+    torch.cuda.synchronize()
+    cap = 1 << 18
+
+    def read_all():
+        recs = []
+        for libname, unit in TRACE_UNITS:
+            fn = getattr(library(libname).lib, f"bfi_trace_read_{unit}")
+            fn.restype = ctypes.c_long
+            buf = np.zeros(2 * cap, dtype=np.uint64)
+            n = fn(buf.ctypes.data_as(ctypes.c_void_p), ctypes.c_long(cap))
+            for i in range(n):
+                key, t = int(buf[2 * i]), int(buf[2 * i + 1])
+                recs.append((key >> 32, (key >> 28) & 0xF, t, unit))
+        return recs
+
+    read_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    one()
+    e1.record()
+    torch.cuda.synchronize()
+    recs = read_all()
+    grids = {}
+    for gid, what, t, unit in recs:
+        d = grids.setdefault(gid, {"unit": unit, "t": {0: [], 1: [], 2: []}})
+        d["t"][what].append(t)
+    order = sorted(grids)
+    t00 = min(t for _, _, t, _ in recs)
+    per_layer = (len(order) - 3) // layers if layers else 9     # beside the layers: embedding, final norm, head
+    first = 1 + a.timeline_layer * per_layer
+    print(f"one decode step, batch {a.batch}, {layers} layers of the {a.shape_name} shape: {e0.elapsed_time(e1):.3f} ms with the stamps; "
+          f"{len(order)} kernels, {per_layer} per layer; layer {a.timeline_layer}:")
+    print("| # | source file | blocks | first start | last start | first wait over | last wait over | first end | last end |")
+    print("|---|---|---|---|---|---|---|---|---|")
+
+    def us(xs, fn):
+        return f"{(fn(xs) - t00) / 1e3:.2f}" if xs else "-"
+
+    for i, gid in enumerate(order):
+        if not first <= i < first + per_layer + 1:
+            continue
+        d = grids[gid]
+        print(f"| {i} | {d['unit']} | {len(d['t'][0])} | {us(d['t'][0], min)} | {us(d['t'][0], max)} | {us(d['t'][1], min)} | "
+              f"{us(d['t'][1], max)} | {us(d['t'][2], min)} | {us(d['t'][2], max)} |")
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--timeline", action="store_true", help="print one decode step's kernels on the GPU's clock (see timeline_run)")
+    ap.add_argument("--timeline-layer", type=int, default=6)
     ap.add_argument("--seqs", type=int, default=1, help="kernel mode, prompt attention: prompts of --rows tokens each")
     ap.add_argument("--kernel", default=None, choices=["skinny_gemm", "gemm_tcgen05", "qk_norm_rope", "attention_decode",
                                                        "attention_prefill", "attention_prefill_tcgen05"],
@@ -453,6 +534,9 @@ def main() -> int:
                           "the reference is a Rust workspace: no Rust toolchain or network here to build it, "
                           "pip cannot install it, and its CUDA backend runs no kernel for bf16 weights"}))
         return 0
+    if a.timeline:
+        os.environ["BFI_B200_TRACE"] = "1"
+        return timeline_run(a)
     if a.kernel is not None:
         return kernel_run(a)
     if a.gpus != 1:

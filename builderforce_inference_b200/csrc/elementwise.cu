@@ -72,10 +72,12 @@ __global__ void rmsnorm_kernel(const TX* __restrict__ x, long x_stride, const in
     }
 }
 
-// Single pass for float32 rows whose width is a multiple of 4 and at most 4 * VPT * 256: the row
-// stays in registers between the sum of squares and the scaling, so it is read once.
-template <int VPT>
-__global__ void __launch_bounds__(256)
+// Single pass for float32 rows whose width is a multiple of 4 and at most 4 * VPT * THREADS: the
+// row stays in registers between the sum of squares and the scaling, so it is read once.  Few rows
+// (a decode step) take 256 threads a row; many rows (a prompt) take 128, so that twice as many rows
+// are in flight on an SM and the whole prompt is resident at once.
+template <int VPT, int THREADS>
+__global__ void __launch_bounds__(THREADS)
 rmsnorm_regs_kernel(const float* __restrict__ x, long x_stride, const int* __restrict__ rows,
                     const void* __restrict__ w, int w_dtype, void* __restrict__ out, int out_dtype,
                     long out_stride, int width, float eps) {
@@ -88,7 +90,7 @@ rmsnorm_regs_kernel(const float* __restrict__ x, long x_stride, const int* __res
     float4 wv[VPT];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-        const int j = i * 256 + threadIdx.x;
+        const int j = i * THREADS + threadIdx.x;
         const int c = j * 4;
         wv[i] = j < n4 ? make_float4(load_as_f32(w, w_dtype, c), load_as_f32(w, w_dtype, c + 1), load_as_f32(w, w_dtype, c + 2),
                                      load_as_f32(w, w_dtype, c + 3))
@@ -100,7 +102,7 @@ rmsnorm_regs_kernel(const float* __restrict__ x, long x_stride, const int* __res
     float ss = 0.0f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-        const int j = i * 256 + threadIdx.x;
+        const int j = i * THREADS + threadIdx.x;
         v[i] = j < n4 ? xr[j] : make_float4(0.f, 0.f, 0.f, 0.f);
         ss = fmaf(v[i].x, v[i].x, ss);
         ss = fmaf(v[i].y, v[i].y, ss);
@@ -112,7 +114,7 @@ rmsnorm_regs_kernel(const float* __restrict__ x, long x_stride, const int* __res
     const size_t obase = (size_t)r * out_stride;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-        const int j = i * 256 + threadIdx.x;
+        const int j = i * THREADS + threadIdx.x;
         if (j >= n4) continue;
         const int c = j * 4;
         const float o0 = v[i].x * scale * wv[i].x;
@@ -141,14 +143,24 @@ extern "C" int bfi_rmsnorm(const void* x, int x_dtype, long x_stride, const int*
     const bool vec = x_dtype == BFI_F32 && width % 4 == 0 && x_stride % 4 == 0 && out_stride % 4 == 0 &&
                      ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0 && width <= 4 * 4 * 256;
     if (vec) {
-        const int vpt = (width / 4 + 255) / 256;
-#define BFI_NORM(V)                                                                                             \
-    bfi_launch(rmsnorm_regs_kernel<V>, dim3(n_rows), dim3(256), 0, stream, (const float*)x, x_stride, rows, w,  \
+#define BFI_NORM(V, T)                                                                                             \
+    bfi_launch(rmsnorm_regs_kernel<V, T>, dim3(n_rows), dim3(T), 0, stream, (const float*)x, x_stride, rows, w,    \
                w_dtype, out, out_dtype, out_stride, width, eps)
-        if (vpt <= 1) BFI_NORM(1);
-        else if (vpt == 2) BFI_NORM(2);
-        else if (vpt == 3) BFI_NORM(3);
-        else BFI_NORM(4);
+        const bool many = n_rows > 4 * bfi_sm_count() && width <= 4 * 8 * 128;
+        if (many) {
+            const int vpt = (width / 4 + 127) / 128;
+            if (vpt <= 1) BFI_NORM(1, 128);
+            else if (vpt == 2) BFI_NORM(2, 128);
+            else if (vpt <= 4) BFI_NORM(4, 128);
+            else if (vpt <= 6) BFI_NORM(6, 128);
+            else BFI_NORM(8, 128);
+        } else {
+            const int vpt = (width / 4 + 255) / 256;
+            if (vpt <= 1) BFI_NORM(1, 256);
+            else if (vpt == 2) BFI_NORM(2, 256);
+            else if (vpt == 3) BFI_NORM(3, 256);
+            else BFI_NORM(4, 256);
+        }
 #undef BFI_NORM
         return bfi_check_launch("rmsnorm");
     }

@@ -429,7 +429,7 @@ def kernel_run(a) -> int:
 
 
 TRACE_UNITS = [("core", "elementwise"), ("core", "sampling"), ("core", "gemm_simt"), ("fast", "gemm_tcgen05"),
-               ("fast", "attention_decode")]
+               ("fast", "attention_decode"), ("fast", "attention_prefill_tcgen05")]
 
 
 def timeline_run(a) -> int:
@@ -457,6 +457,18 @@ def timeline_run(a) -> int:
 
     def one():
         eng.step([SequenceStep(s, (5,), (0,)) for s in slots], check=False)
+
+    if a.timeline_prompt:
+        # a prompt step instead: --timeline-prompt tokens, eager launches
+        for s in slots:
+            eng.release(s)
+        prompt = torch.randint(0, 1000, (a.timeline_prompt,), generator=g).tolist()
+
+        def one():                                                     # noqa: F811
+            s = eng.acquire()
+            eng.step([SequenceStep(s, prompt, (len(prompt) - 1,))], check=False)
+            torch.cuda.synchronize()
+            eng.release(s)
 
     for _ in range(6):
         one()
@@ -490,7 +502,8 @@ def timeline_run(a) -> int:
     t00 = min(t for _, _, t, _ in recs)
     per_layer = (len(order) - 3) // layers if layers else 9     # beside the layers: embedding, final norm, head
     first = 1 + a.timeline_layer * per_layer
-    print(f"one decode step, batch {a.batch}, {layers} layers of the {a.shape_name} shape: {e0.elapsed_time(e1):.3f} ms with the stamps; "
+    what = f"one prompt step of {a.timeline_prompt} tokens" if a.timeline_prompt else f"one decode step, batch {a.batch}"
+    print(f"{what}, {layers} layers of the {a.shape_name} shape: {e0.elapsed_time(e1):.3f} ms with the stamps; "
           f"{len(order)} kernels, {per_layer} per layer; layer {a.timeline_layer}:")
     print("| # | source file | blocks | first start | last start | first wait over | last wait over | first end | last end |")
     print("|---|---|---|---|---|---|---|---|---|")
@@ -511,6 +524,7 @@ def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--timeline", action="store_true", help="print one decode step's kernels on the GPU's clock (see timeline_run)")
     ap.add_argument("--timeline-layer", type=int, default=6)
+    ap.add_argument("--timeline-prompt", type=int, default=0, help="with --timeline: a prompt step of this many tokens instead")
     ap.add_argument("--seqs", type=int, default=1, help="kernel mode, prompt attention: prompts of --rows tokens each")
     ap.add_argument("--kernel", default=None, choices=["skinny_gemm", "gemm_tcgen05", "qk_norm_rope", "attention_decode",
                                                        "attention_prefill", "attention_prefill_tcgen05"],

@@ -625,6 +625,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             __threadfence();
         }
     }
+    BFI_TRACE_END();
 }
 
 template <int D>
@@ -724,3 +725,5 @@ extern "C" int bfi_attention_prefill_tcgen05_bf16_wait_probe(const void* qkv, lo
                                        cu_seqlens, seq_slot, seq_start, n_seqs, n_tokens, max_seq_tokens, n_q, n_kv, d, window,
                                        scale, status, stream, TcWaits{spin_limit, hold_producer ? 1 : 0});
 }
+
+BFI_TRACE_EXPORT(attention_prefill_tcgen05)

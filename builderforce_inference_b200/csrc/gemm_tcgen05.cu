@@ -563,6 +563,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
+    BFI_TRACE_END();
 }
 
 // ------------------------------------------------------------------------------------------

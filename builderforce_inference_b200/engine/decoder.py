@@ -110,15 +110,38 @@ class Decoder:
     def graph_safe(self) -> bool:
         return all(b.all_graph_safe() for b in self.blocks) and self.final_norm.all_graph_safe()
 
+    def stages(self) -> List[tuple]:
+        """A single-token step as stages that may (True) or may not be captured in a CUDA graph:
+        ``("embed",)``, ``("runs", first, last)`` for schedule entries ``first .. last-1``, and
+        ``("logits",)``, each with its flag; neighbours with the same flag are one stage.  A model
+        whose parts are all graph-safe is one stage."""
+        ops: List[tuple] = [(True, ("embed",))]
+        for i, run in enumerate(self.spec.schedule):
+            ops.append((self.blocks[run.layer].all_graph_safe(), ("runs", i, i + 1)))
+        ops.append((self.final_norm.all_graph_safe(), ("logits",)))
+        out: List[tuple] = []
+        for safe, op in ops:
+            if out and out[-1][0] == safe:
+                last = out[-1][1]
+                if op[0] == "runs" and last and last[-1][0] == "runs":
+                    last[-1] = ("runs", last[-1][1], op[2])
+                else:
+                    last.append(op)
+            else:
+                out.append((safe, [op]))
+        return out
+
     # ---- compute ---------------------------------------------------------------------
     def embed(self, ctx) -> torch.Tensor:
         x = ctx.rows("residual", self.spec.width, torch.float32)
         ops.embed_rows(self.embedding, ctx.token_ids[:ctx.n_tokens], x, ctx.status)
         return x
 
-    def run_layers(self, ctx, x: torch.Tensor, cache) -> None:
-        for i, run in enumerate(self.spec.schedule):
-            self.blocks[run.layer].forward(ctx, x, cache.run_cache(i))
+    def run_layers(self, ctx, x: torch.Tensor, cache, first: int = 0, last: Optional[int] = None) -> None:
+        """Schedule entries ``first .. last-1`` (all of them by default)."""
+        last = len(self.spec.schedule) if last is None else last
+        for i in range(first, last):
+            self.blocks[self.spec.schedule[i].layer].forward(ctx, x, cache.run_cache(i))
 
     def logits(self, ctx, x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
         """Final norm and head at the given rows of ``x``; ``out`` is float32 ``[len(rows), vocab]``."""

@@ -151,10 +151,13 @@ def pages_bucket(most_pages: int, limit: int) -> int:
 
 
 class _DecodeGraphs:
-    """The captured single-token steps of one padded batch size: one graph per page-count bucket
-    (kernels cut their work by the most pages a sequence of the step holds), all over the same
-    index arrays and logits.  Every bucket is captured when the batch size is first seen, so no
-    capture falls into the middle of a generation."""
+    """The captured single-token steps of one padded batch size: per page-count bucket (kernels
+    cut their work by the most pages a sequence of the step holds) the step's stages, all over
+    the same index arrays and logits.  A stage whose parts are all graph-safe is a CUDA graph; a
+    stage with a part that is not (it reads the host's lists of slots and lengths, or launches
+    shapes that depend on them) runs as it is written, between the graphs.  Every bucket is
+    captured when the batch size is first seen, so no capture falls into the middle of a
+    generation."""
 
     def __init__(self, engine: "Engine", batch: int):
         self.batch = batch
@@ -164,7 +167,8 @@ class _DecodeGraphs:
         self.rows = torch.arange(batch, dtype=torch.int32, device=dev)
         # every row starts as padding (slot -1), so the runs below touch no sequence's cache
         engine._fill_meta(self.meta, [], [], [], [0], batch, batch)
-        self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self.stages = engine.decoder.stages()
+        self.graphs: Dict[int, list] = {}           # bucket -> [CUDAGraph or None per stage]
         self.n_kernels: Dict[int, int] = {}
         limit = engine.cache.n_blocks
         buckets, b = [], 1
@@ -173,23 +177,55 @@ class _DecodeGraphs:
             if b >= limit:
                 break
             b *= PAGE_BUCKETS_STEP
-        # eager runs first: they load kernels, size the workspace and set launch attributes
+        # eager runs first (no sequence: the host lists are empty): they load kernels, size the
+        # workspace and set launch attributes
         for b in buckets:
-            ctx = engine._context_from_meta(self.meta, batch, batch, 1, None)
-            ctx.pages_bucket = b
-            engine._forward(ctx, self.rows, self.logits)
+            ctx = self.context(engine, b, ([], [], []))
+            for _, ops in self.stages:
+                self.run_ops(engine, ctx, ops)
         torch.cuda.synchronize(dev)
         self.stamp = engine._stamp()
         for b in buckets:
-            ctx = engine._context_from_meta(self.meta, batch, batch, 1, None)
-            ctx.pages_bucket = b
+            ctx = self.context(engine, b, None)
             ctx.capturing = True
-            graph = torch.cuda.CUDAGraph()
-            before = total_calls()
-            with torch.cuda.graph(graph):
-                engine._forward(ctx, self.rows, self.logits)
-            self.graphs[b] = graph
-            self.n_kernels[b] = total_calls() - before      # launches one replay stands for
+            graphs, count = [], 0
+            for safe, ops in self.stages:
+                if not safe:
+                    graphs.append(None)
+                    continue
+                graph = torch.cuda.CUDAGraph()
+                before = total_calls()
+                with torch.cuda.graph(graph):
+                    self.run_ops(engine, ctx, ops)
+                count += total_calls() - before
+                graphs.append(graph)
+            self.graphs[b] = graphs
+            self.n_kernels[b] = count                   # launches the replays of one step stand for
+
+    def context(self, engine: "Engine", bucket: int, host) -> StepContext:
+        ctx = engine._context_from_meta(self.meta, self.batch, self.batch, 1, host)
+        ctx.pages_bucket = bucket
+        return ctx
+
+    def run_ops(self, engine: "Engine", ctx: StepContext, ops) -> None:
+        x = ctx.rows("residual", engine.spec.width, torch.float32)
+        for op in ops:
+            if op[0] == "embed":
+                engine.decoder.embed(ctx)
+            elif op[0] == "runs":
+                engine.decoder.run_layers(ctx, x, engine.cache, op[1], op[2])
+            else:
+                engine.decoder.logits(ctx, x, self.rows, self.logits)
+
+    def replay(self, engine: "Engine", bucket: int, host) -> None:
+        ctx = None
+        for (safe, ops), graph in zip(self.stages, self.graphs[bucket]):
+            if graph is not None:
+                graph.replay()
+            else:
+                if ctx is None:
+                    ctx = self.context(engine, bucket, host)
+                self.run_ops(engine, ctx, ops)
 
 
 class Engine:
@@ -226,7 +262,10 @@ class Engine:
         self.workspace = Workspace(device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.prefill_chunk_tokens = max(PAGE_TOKENS, int(prefill_chunk_tokens))
-        self.use_graphs = bool(use_graphs) and self.decoder.graph_safe()
+        # single-token steps are replayed from CUDA graphs, stage by stage: the stages whose parts are
+        # all graph-safe (for a model of such parts only, the whole step is one graph)
+        self.use_graphs = bool(use_graphs) and any(safe and any(op[0] == "runs" for op in ops)
+                                                   for safe, ops in self.decoder.stages())
         self._graphs: Dict[int, _DecodeGraphs] = {}
         self._pinned = PinnedRings()
         self.last_h2d_bytes = 0        # bytes of index arrays the last step copied to the device
@@ -387,7 +426,7 @@ class Engine:
             self._fill_meta(g.meta, tokens, starts, slots, list(range(b + 1)), padded, padded)
             if device_tokens is not None:
                 g.meta[:b].copy_(device_tokens, non_blocking=True)
-            g.graphs[bucket].replay()
+            g.replay(self, bucket, (slots, starts, [1] * b))
             self.graph_kernel_launches += g.n_kernels[bucket]
             logits = g.logits
         else:

@@ -138,7 +138,9 @@ def test_toy_architecture_with_state_repeated_layers_and_a_shared_cache():
         w = {k: v.float() for k, v in P.read_safetensors(os.path.join(folder, "model.safetensors")).items()}
         assert "blocks.1.mix" in w and "blocks.2.k_proj" not in w
         eng = Engine.load(folder, dtype="float32", max_tokens=1024)
-        assert not eng.use_graphs                      # the toy mixer is not graph-safe: never captured
+        # the toy mixer is not graph-safe: its two runs stay as written, the attention layers around
+        # them are replayed from CUDA graphs
+        assert eng.use_graphs and [safe for safe, _ in eng.decoder.stages()] == [True, False, True, False, True]
         assert len(eng.cache.kv_groups) == 1 and eng.cache.kv_groups[0].runs == [0, 2]
         assert len(eng.cache.state_groups) == 1 and eng.cache.state_groups[0].runs == [1, 3]
         g = torch.Generator().manual_seed(1)
@@ -172,6 +174,11 @@ def test_toy_architecture_with_state_repeated_layers_and_a_shared_cache():
         for i, r in enumerate(refs):
             assert rel_err(torch.cat(got[i]), r) < 1e-4, i
         eng.cache.check()
+        # the same token by token without any graph gives the same logits
+        plain = Engine.load(folder, dtype="float32", max_tokens=1024, use_graphs=False)
+        a, b = eng.acquire(), plain.acquire()
+        for t in prompts[2][:12]:
+            assert torch.equal(eng.step([S(a, [t], [0])]), plain.step([S(b, [t], [0])]))
     finally:
         undo()
     from builderforce_inference_b200 import registered_architectures
@@ -498,6 +505,7 @@ def test_toy_mixer_with_keys_and_values_and_a_state_of_its_own():
         write_model_folder(HYBRID_CONFIG, 8, folder, torch.float32)
         w = {k: v.float() for k, v in P.read_safetensors(os.path.join(folder, "model.safetensors")).items()}
         eng = Engine.load(folder, dtype="float32", max_tokens=1024)
+        assert eng.use_graphs and [safe for safe, _ in eng.decoder.stages()] == [True, False, True, False, True]
         # the three runs' keys and values share one group; the two hybrid runs' states another
         assert [g.keys for g in eng.cache.kv_groups] == [[(0, 0), (1, 0), (2, 0)]]
         assert [g.keys for g in eng.cache.state_groups] == [[(0, 1), (2, 1)]]

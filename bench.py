@@ -602,7 +602,7 @@ def main() -> int:
             decode_points[f"b{b}_after_prompt"] = point(after, pk)
             deep = decode_run(model, b, deep_steps, 3, seed=5, lens=[deep_start] * b)
             decode_points[f"b{b}_ctx{CONTEXT}"] = point(deep, pk)
-        e1 = e2e_run(model, 1, min(a.steps, 32), warmup, seed=6)
+        e1 = e2e_run(model, 1, min(a.steps, 32), warmup, seed=4)          # the prompt of the batch-1 point above
         e2e_b1 = {"value": round(e1["tok_s"], 1), "unit": "tokens/s", "h2d_bytes_per_step": e1["h2d"],
                   "d2h_bytes_per_step": e1["d2h"]}
         pf = prefill_run(model, PREFILL_TOKENS, 5, a.layers, shape_cfg, breakdown=True)

@@ -7,7 +7,10 @@ to the reference project).  Shapes follow the reference: activations are
 (``crates/bfi-models/src/state.rs:52-59``: every activation and the cache are
 f32); ``dtype=torch.float64`` gives a tighter oracle for the 32-bit tests.
 
-This file shares no code with the product package.
+This file shares no code with the product package.  It rests on the reference's formulas alone:
+the reference is a Rust workspace that cannot be built or imported here (no Rust toolchain, no
+network) and ships no numeric golden for this architecture, so there is nothing to compare it
+with but the cited lines themselves.
 """
 from __future__ import annotations
 

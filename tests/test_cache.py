@@ -167,6 +167,12 @@ def test_random_traffic_never_loses_or_duplicates_anything():
             s = rng.choice(list(live))
             c.release(s)
             del live[s]
+        elif r < 0.5 and live:
+            # wind a sequence back: the windowed group refuses and nothing may change
+            s = rng.choice(list(live))
+            if live[s] > 0:
+                with pytest.raises(CacheError, match="rewind unsupported"):
+                    c.rewind(s, live[s] // 2)
         elif live:
             batch = rng.sample(list(live), rng.randint(1, len(live)))
             counts = [rng.choice([1, 1, 1, 5, 64, 100]) for _ in batch]
@@ -277,3 +283,47 @@ def test_cache_sized_from_a_byte_budget():
     c = SequenceCache(needs, [None, None, 0], p.max_tokens, 256, torch.float32, CPU, initial_slots=10)
     assert sum(g.storage.numel() * 4 for g in c.kv_groups) == p.kv_bytes
     assert c.bytes_per_token() == p.bytes_per_token and c.state_bytes_per_slot() == p.state_bytes_per_slot
+
+
+def test_random_traffic_with_rewinds():
+    rng = random.Random(3)
+    c = make(needs=[KVNeed(1, 16), KVNeed(2, 16)], max_tokens=64 * 20, max_seq_len=400, slots=2)
+    live = {}
+    for it in range(800):
+        r = rng.random()
+        if r < 0.2 and len(live) < 6:
+            try:
+                live[c.acquire()] = 0
+            except CacheError:
+                pass
+        elif r < 0.35 and live:
+            s = rng.choice(list(live))
+            c.release(s)
+            del live[s]
+        elif r < 0.55 and live:
+            s = rng.choice(list(live))
+            keep = rng.randint(0, live[s])
+            c.rewind(s, keep)
+            live[s] = keep
+        elif live:
+            batch = rng.sample(list(live), rng.randint(1, len(live)))
+            counts = [rng.choice([1, 1, 7, 64, 90]) for _ in batch]
+            try:
+                c.begin_step(batch, counts)
+            except CacheError as e:
+                assert "context_exceeded" in str(e) or "cache full" in str(e)
+                continue
+            c.end_step(batch, counts)
+            for s, n in zip(batch, counts):
+                live[s] += n
+        c.check()
+        assert {s: c.length(s) for s in live} == live
+        for g in c.kv_groups:
+            assert g.table.held_pages() == sum((n + PAGE_TOKENS - 1) // PAGE_TOKENS for n in live.values())
+            for s, n in live.items():
+                row = g.table.rows[s]
+                assert len(row) == (n + PAGE_TOKENS - 1) // PAGE_TOKENS or (len(row) >= (n + PAGE_TOKENS - 1) // PAGE_TOKENS)
+                assert g.block_host[s, :len(row)].tolist() == row and all(p >= 0 for p in row[:(n + PAGE_TOKENS - 1) // PAGE_TOKENS])
+    for s in list(live):
+        c.release(s)
+    assert all(g.table.pool.n_free == g.table.pool.capacity for g in c.kv_groups) and c.slots.n_held == 0

@@ -49,7 +49,8 @@ def _engine_flags(p: argparse.ArgumentParser) -> None:
 
 
 def _sample_flags(p: argparse.ArgumentParser) -> None:
-    p.add_argument("--max-tokens", type=int, default=256, help="0: until the context is full")
+    p.add_argument("--max-tokens", "--max-new-tokens", dest="max_tokens", type=int, default=256,
+                   help="tokens to generate per prompt; 0: until the context is full")
     p.add_argument("--temperature", type=float, default=0.0, help="0: greedy")
     p.add_argument("--top-k", type=int, default=0)
     p.add_argument("--top-p", type=float, default=1.0)
@@ -133,7 +134,11 @@ def cmd_bench(a) -> int:
         return [torch.randint(0, vocab, (max(n, 1),), generator=g).tolist() for _ in range(batch)]
 
     pp_prompts = prompts(a.pp)
-    tg_prompts = prompts(a.ctx if a.ctx else 2)
+    if a.prompt_len_max:
+        lens = torch.randint(max(a.prompt_len_min, 1), a.prompt_len_max + 1, (batch,), generator=g).tolist()
+        tg_prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lens]
+    else:
+        tg_prompts = prompts(a.ctx if a.ctx else 2)
 
     def timed(ps, n_new):
         model.generate_batch(ps, SampleParams(max_tokens=n_new), ignore_eos=True)       # warm-up
@@ -197,6 +202,9 @@ def main(argv=None) -> int:
     b.add_argument("--batch", type=int, default=1, help="sequences run together")
     b.add_argument("--ctx", type=int, default=0, help="generate from prompts of this many tokens (0: two tokens)")
     b.add_argument("--reps", type=int, default=1, help="timed repetitions of each test (the median is reported)")
+    b.add_argument("--prompt-len-min", type=int, default=0,
+                   help="with --prompt-len-max: the generation test starts from prompts of unequal lengths, uniform between the two")
+    b.add_argument("--prompt-len-max", type=int, default=0)
     _engine_flags(b)
     b.set_defaults(fn=cmd_bench)
     w = sub.add_parser("random", help="write a model folder with random weights")

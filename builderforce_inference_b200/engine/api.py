@@ -173,6 +173,28 @@ class Model:
         last = self.stepper.last_logits
         return GreedyTrace(ids, last[-1].detach().clone() if last is not None and last.shape[0] else torch.empty(0))
 
+    # ---- the step function and the slots, for callers that drive the model themselves ------------
+    def step(self, seqs: Sequence[SequenceStep], check: bool = True) -> torch.Tensor:
+        """``Engine.step``: the given tokens of the given sequences as one batch, float32 logits at
+        the wanted places."""
+        return self.engine.step(seqs, check=check)
+
+    def alloc_slot(self) -> int:
+        return self.engine.acquire()
+
+    def free_slot(self, slot: int) -> None:
+        self.engine.release(slot)
+
+    @property
+    def config(self):
+        """The configuration the model was built from, as its architecture's typed, read-only object
+        (None for a model whose architecture registered no configuration class)."""
+        from ..registry import architecture_for
+        if self.engine.config is None:
+            return None
+        cls = architecture_for(self.engine.config).config_class
+        return cls.from_dict(self.engine.config) if hasattr(cls, "from_dict") else self.engine.config
+
     # accessors in the reference's names (engine/mod.rs:477-503)
     def n_layer(self) -> int:
         return len(self.engine.spec.layers)

@@ -140,6 +140,25 @@ def test_sampling_is_seeded_and_follows_the_plain_distribution(params):
             ids.append(tok)
 
 
+def test_model_exposes_the_step_function_the_slots_and_its_configuration():
+    from builderforce_inference_b200 import Qwen3Config, SequenceStep, registry
+    model = load("B", "float32")
+    cfg = model.config
+    assert isinstance(cfg, Qwen3Config) and cfg.head_dim == 32 and cfg.num_key_value_heads == 3
+    with pytest.raises(Exception):
+        cfg.head_dim = 64                                   # read-only
+    assert registry() == ["Qwen3ForCausalLM", "qwen3"]
+    assert (model.n_layer(), model.n_vocab(), model.n_ctx(), model.n_embd()) == (3, 384, 256, 96)
+    folder = model_folder("B", torch.float32)
+    p = random_prompts(384, [9], seed=1)[0]
+    slot = model.alloc_slot()
+    got = model.step([SequenceStep(slot, p, [8])]).cpu()
+    from helpers import plain_logits, rel_err
+    assert rel_err(got, plain_logits(folder, p)[8:9]) < 1e-4
+    model.free_slot(slot)
+    assert model.engine.cache.slots.n_held == 0
+
+
 def test_seeded_temperature_sampling_in_bfloat16():
     """Tiny B at temperature 0.8, seeded, in bfloat16.  The engine's logits differ from the plain
     ones by at most e = BF16_TOL * max|logit|, so every probability moves by a factor within
@@ -185,7 +204,7 @@ def test_command_line_run_and_bench():
     cfg, w = plain_model(folder)
     prompt = [5, 9, 200, 31]
     r = subprocess.run([sys.executable, "-m", "builderforce_inference_b200", "run", folder, "5 9 200,31",
-                        "--dtype", "float32", "--max-tokens", "12", "--ignore-eos"], cwd=ROOT, capture_output=True,
+                        "--dtype", "float32", "--max-new-tokens", "12", "--ignore-eos"], cwd=ROOT, capture_output=True,
                        text=True, timeout=600)
     assert r.returncode == 0, r.stderr[-2000:]
     assert [int(t) for t in r.stdout.split()] == P.greedy_generate(w, cfg, prompt, 12)
@@ -196,7 +215,8 @@ def test_command_line_run_and_bench():
     rates = [float(line.split("|")[4]) for line in r.stdout.splitlines() if "| pp64 |" in line or "| tg16 |" in line]
     assert len(rates) == 2 and all(math.isfinite(x) and x > 0 for x in rates), r.stdout
     r = subprocess.run([sys.executable, "-m", "builderforce_inference_b200", "bench", folder, "--pp", "32", "--tg",
-                        "8", "--batch", "3", "--ctx", "20", "--reps", "2", "--json", "--dtype", "float32"], cwd=ROOT,
+                        "8", "--batch", "3", "--prompt-len-min", "5", "--prompt-len-max", "40", "--reps", "2", "--json",
+                        "--dtype", "float32"], cwd=ROOT,
                        capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stderr[-2000:]
     rates = json.loads(r.stdout.strip().splitlines()[-1])

@@ -88,9 +88,20 @@ def test_replay_three_ways(name, dtype):
                 assert e < tol(dtype), f"{kind}: request {i} (len {lens[i]}) first wrong position {t}: {e:.3e}"
     # the three cuttings agree with each other more closely than with the plain implementation
     close = 5e-6 if dtype == "float32" else tol(dtype)
+    flips = 0
     for i in range(len(prompts)):
         assert rel_err(results["last32"][i], results["whole"][i]) < close
         assert rel_err(results["batches"][i], results["whole"][i]) < close
+        # the same best token at each of the last 32 positions from all three schedules; in
+        # bfloat16 a near-tie of the plain logits (top-2 gap under 1 % of the largest) may turn
+        for kind in ("last32", "batches"):
+            a, b = results[kind][i][-32:].argmax(dim=-1), results["whole"][i][-32:].argmax(dim=-1)
+            for t in (a != b).nonzero().flatten().tolist():
+                row = refs[i][-32:][t] if len(prompts[i]) >= 32 else refs[i][t]
+                top2 = row.topk(2).values
+                assert dtype == "bfloat16" and float(top2[0] - top2[1]) < 1e-2 * float(row.abs().max()), (kind, i, t)
+                flips += 1
+    assert flips <= 2, flips
 
 
 def test_steps_without_wanted_places_write_no_file_and_empty_home_works(tmp_path):

@@ -255,64 +255,46 @@ attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
     BFI_TRACE_END();
 }
 
-// Merges the ranges of every (sequence, head) in range order.
-template <int D>
+// Merges the ranges of every (sequence, head) in range order.  CAP: the most ranges a sequence
+// can have here (8, 16 or 32): every load of a thread is issued before the first is used, so the
+// kernel costs one trip to memory after its wait; the sequence's slot and position, which were
+// there before the step began, are fetched ahead of the wait.
+template <int D, int CAP>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                                               bf16* __restrict__ out, long out_stride, int n_q, int max_splits, int window) {
     pdl_trigger();
-    pdl_wait();
     const int seq = blockIdx.y, head = blockIdx.x;
-    if (seq_slot[seq] < 0) return;
+    const int slot = seq_slot[seq];
     const int pos = seq_start[seq];
+    pdl_wait();
+    if (slot < 0) return;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int n_pages = pos / AD_TILE - lo / AD_TILE + 1;
     const int pps = decode_pages_per_split(n_pages, max_splits);
     const int n_splits = (n_pages + pps - 1) / pps;
     if (n_splits == 1) return;                            // the first kernel wrote the output itself
     const size_t base = ((size_t)seq * n_q + head) * max_splits;
-    if (n_splits <= 8) {
-        // few ranges: every load of this thread is issued before the first is used, so the kernel
-        // costs one trip to memory after its wait instead of three
-        float ms[8], ls[8], os[8];
-        const int e = threadIdx.x;                        // blockDim.x == D here
+    float ms[CAP], ls[CAP], os[CAP];
+    const int e = threadIdx.x;                            // blockDim.x == D
 #pragma unroll
-        for (int s = 0; s < 8; ++s) {
-            const bool have = s < n_splits;
-            ms[s] = have ? part_ml[(base + s) * 2] : -INFINITY;
-            ls[s] = have ? part_ml[(base + s) * 2 + 1] : 0.0f;
-            os[s] = have ? part_o[(base + s) * D + e] : 0.0f;
-        }
-        float m = ms[0];
+    for (int s = 0; s < CAP; ++s) {
+        const bool have = s < n_splits;
+        ms[s] = have ? part_ml[(base + s) * 2] : -INFINITY;
+        ls[s] = have ? part_ml[(base + s) * 2 + 1] : 0.0f;
+        os[s] = have ? part_o[(base + s) * D + e] : 0.0f;
+    }
+    float m = ms[0];
 #pragma unroll
-        for (int s = 1; s < 8; ++s) m = fmaxf(m, ms[s]);
-        float l = 0.0f, acc = 0.0f;
+    for (int s = 1; s < CAP; ++s) m = fmaxf(m, ms[s]);
+    float l = 0.0f, acc = 0.0f;
 #pragma unroll
-        for (int s = 0; s < 8; ++s) {
-            const float f = (ms[s] == -INFINITY) ? 0.0f : fast_exp2(ms[s] - m);
-            l += ls[s] * f;
-            acc = fmaf(os[s], f, acc);
-        }
-        out[(size_t)seq * out_stride + (size_t)head * D + e] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
-        return;
+    for (int s = 0; s < CAP; ++s) {
+        const float f = (ms[s] == -INFINITY) ? 0.0f : fast_exp2(ms[s] - m);
+        l += ls[s] * f;
+        acc = fmaf(os[s], f, acc);
     }
-    float m = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
-    float l = 0.0f;
-    for (int s = 0; s < n_splits; ++s) {
-        const float ms = part_ml[(base + s) * 2];
-        l += part_ml[(base + s) * 2 + 1] * ((ms == -INFINITY) ? 0.0f : fast_exp2(ms - m));
-    }
-    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-    for (int e = threadIdx.x; e < D; e += blockDim.x) {
-        float acc = 0.0f;
-#pragma unroll 4
-        for (int s = 0; s < n_splits; ++s) {
-            const float ms = part_ml[(base + s) * 2];
-            acc = fmaf(part_o[(base + s) * D + e], (ms == -INFINITY) ? 0.0f : fast_exp2(ms - m), acc);
-        }
-        out[(size_t)seq * out_stride + (size_t)head * D + e] = __float2bfloat16_rn(acc * inv);
-    }
+    out[(size_t)seq * out_stride + (size_t)head * D + e] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
 }
 
 template <int D>
@@ -338,14 +320,18 @@ static int launch_decode(const void* q, long q_stride, void* out, long out_strid
                scale_log2, head_chunks, part_o, part_ml);
     int rc = bfi_check_launch("attention_decode");
     if (rc || max_splits == 1) return rc;
-    bfi_launch(attention_decode_merge_kernel<D>, dim3(n_q, n_seqs), dim3(D), 0, stream,
-               (const float*)part_o, (const float*)part_ml, seq_slot, seq_start, (bf16*)out, out_stride, n_q, max_splits,
-               window);
+#define BFI_MERGE(CAP)                                                                                                   \
+    bfi_launch(attention_decode_merge_kernel<D, CAP>, dim3(n_q, n_seqs), dim3(D), 0, stream, (const float*)part_o,        \
+               (const float*)part_ml, seq_slot, seq_start, (bf16*)out, out_stride, n_q, max_splits, window)
+    if (max_splits <= 8) BFI_MERGE(8);
+    else if (max_splits <= 16) BFI_MERGE(16);
+    else BFI_MERGE(32);
+#undef BFI_MERGE
     return bfi_check_launch("attention_decode_merge");
 }
 
 // Returns 0 on success, 1 on error, 2 when the shape is not taken (nothing launched).
-// Every sequence's pages are cut into at most `max_splits` ranges.  With max_splits > 1 the caller
+// Every sequence's pages are cut into at most `max_splits` (up to 32) ranges.  With max_splits > 1 the caller
 // gives part_o [n_seqs*n_q*max_splits*d] and part_ml [n_seqs*n_q*max_splits*2] floats.
 extern "C" int bfi_attention_decode_bf16(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
                                          const void* v_pages, const int* block_table, int table_stride,
@@ -354,7 +340,7 @@ extern "C" int bfi_attention_decode_bf16(const void* q, long q_stride, void* out
                                          cudaStream_t stream) {
     BFI_REQUIRE(n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_decode: %d query heads do not divide into %d kv heads",
                 n_q, n_kv);
-    BFI_REQUIRE(window >= 0 && max_splits >= 1 && max_splits <= 65535, "attention_decode: bad window or split count");
+    BFI_REQUIRE(window >= 0 && max_splits >= 1 && max_splits <= 32, "attention_decode: bad window or split count (1..32)");
     if (n_seqs <= 0) return 0;
     if (d != 64 && d != 128) return 2;
     if (q_stride % 8 != 0 || ((uintptr_t)q & 15) || n_seqs > 65535) return 2;

@@ -93,7 +93,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    float c_pre0 = 0.0f, c_pre1 = 0.0f, c_pre2 = 0.0f, c_pre3 = 0.0f;     // epilogue threads: see there
+    float c_pre[4] = {0.0f, 0.0f, 0.0f, 0.0f};                            // epilogue threads: see there
 
     if (warp == 0) {
         // ---------------- TMA producer
@@ -166,10 +166,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const int per_rank = (BT + ksplit - 1) / ksplit;
             const int j0 = (int)blockIdx.z * per_rank;
             const float* c_in = reinterpret_cast<const float*>(C);
-            if (0 < per_rank && j0 + 0 < BT && m0 + j0 + 0 < M) c_pre0 = c_in[(size_t)(m0 + j0 + 0) * ldc + n];
-            if (1 < per_rank && j0 + 1 < BT && m0 + j0 + 1 < M) c_pre1 = c_in[(size_t)(m0 + j0 + 1) * ldc + n];
-            if (2 < per_rank && j0 + 2 < BT && m0 + j0 + 2 < M) c_pre2 = c_in[(size_t)(m0 + j0 + 2) * ldc + n];
-            if (3 < per_rank && j0 + 3 < BT && m0 + j0 + 3 < M) c_pre3 = c_in[(size_t)(m0 + j0 + 3) * ldc + n];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (u < per_rank && j0 + u < BT && m0 + j0 + u < M) c_pre[u] = c_in[(size_t)(m0 + j0 + u) * ldc + n];
         }
         if (n_kb > 0) {
             ok = MBAR_WAIT(tmem_full, 0);
@@ -197,24 +196,37 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 for (int j = 0; j < 16; ++j) part[(c * 16 + j) * TC_ROWS + n_local] = v[j];
             }
         } else if (ok) {
+            // 16 tokens at a time.  All of a chunk's values are computed (and, when adding, all the old
+            // values fetched) before the first store, without a branch between them: one warp per
+            // scheduler has nothing else to cover the latency of a shuffle, an exponential or a load.
 #pragma unroll 1
             for (int c = 0; c < BT / 16; ++c) {
-                if (m0 + c * 16 >= M) break;
+                const int m_c = m0 + c * 16;
+                if (m_c >= M) break;
+                const int rows_here = min(16, M - m_c);
                 float v[16];
                 tmem_ld16(lane_addr + c * 16, v);
+                if (epilogue == EPI_SWIGLU) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int m = m0 + c * 16 + j;
-                    if (epilogue == EPI_SWIGLU) {
-                        const float up = __shfl_down_sync(0xffffffffu, v[j], 1);
-                        if (m < M && (lane & 1) == 0 && n + 1 < N)
-                            store_from_f32(C, c_dtype, (size_t)m * ldc + (n >> 1), silu_mul_tc(v[j], up));
-                    } else if (m < M && n < N) {
-                        const size_t o = (size_t)m * ldc + n;
-                        if (epilogue == EPI_ACCUMULATE)
-                            reinterpret_cast<float*>(C)[o] += v[j];
-                        else
-                            store_from_f32(C, c_dtype, o, v[j]);
+                    for (int j = 0; j < 16; ++j) v[j] = silu_mul_tc(v[j], __shfl_down_sync(0xffffffffu, v[j], 1));
+                    if ((lane & 1) == 0 && n + 1 < N) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (j < rows_here) store_from_f32(C, c_dtype, (size_t)(m_c + j) * ldc + (n >> 1), v[j]);
+                    }
+                } else if (n < N) {
+                    if (epilogue == EPI_ACCUMULATE) {
+                        float* c_io = reinterpret_cast<float*>(C) + (size_t)m_c * ldc + n;
+                        float old[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) old[j] = j < rows_here ? c_io[(size_t)j * ldc] : 0.0f;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (j < rows_here) c_io[(size_t)j * ldc] = old[j] + v[j];
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (j < rows_here) store_from_f32(C, c_dtype, (size_t)(m_c + j) * ldc + n, v[j]);
                     }
                 }
             }
@@ -238,33 +250,45 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 const uint32_t local = smem_u32(smem);
                 asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[r]) : "r"(local), "r"(r < ksplit ? r : 0));
             }
-            for (int j = rank * per_rank; j < min(BT, (rank + 1) * per_rank); ++j) {
-                const int m = m0 + j;
-                if (m >= M) break;
-                // all splits' loads first, then the sum in split order
-                float x[8];
+            // four tokens at a time: every split's partial value of all four (and, when adding, the old
+            // values beyond the four fetched before the products) is asked for before the first is
+            // used, then each token's sum is taken in split order
+            const int j_beg = rank * per_rank;
+            const int j_end = min(min(BT, (rank + 1) * per_rank), M - m0);
+#pragma unroll 1
+            for (int j0 = j_beg; j0 < j_end; j0 += 4) {
+                float x[4][8], old[4];
 #pragma unroll
-                for (int r = 0; r < 8; ++r) {
-                    x[r] = 0.0f;
-                    if (r < ksplit)
-                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(x[r]) : "r"(remote[r] + (uint32_t)(j * TC_ROWS + n_local) * 4));
+                for (int u = 0; u < 4; ++u) {
+                    const bool live = j0 + u < j_end;
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) {
+                        x[u][r] = 0.0f;
+                        if (live && r < ksplit)
+                            asm volatile("ld.shared::cluster.f32 %0, [%1];"
+                                         : "=f"(x[u][r])
+                                         : "r"(remote[r] + (uint32_t)((j0 + u) * TC_ROWS + n_local) * 4));
+                    }
+                    old[u] = c_pre[u];
+                    if (epilogue == EPI_ACCUMULATE && j0 > j_beg && live && n < N)
+                        old[u] = reinterpret_cast<const float*>(C)[(size_t)(m0 + j0 + u) * ldc + n];
                 }
-                float v = 0.0f;
 #pragma unroll
-                for (int r = 0; r < 8; ++r) v += x[r];
-                if (epilogue == EPI_SWIGLU) {
-                    const float up = __shfl_down_sync(0xffffffffu, v, 1);
-                    if ((lane & 1) == 0 && n + 1 < N)
-                        store_from_f32(C, c_dtype, (size_t)m * ldc + (n >> 1), silu_mul_tc(v, up));
-                } else if (n < N) {
-                    const size_t o = (size_t)m * ldc + n;
-                    if (epilogue == EPI_ACCUMULATE) {
-                        const int jj = j - rank * per_rank;
-                        const float old = jj == 0 ? c_pre0 : jj == 1 ? c_pre1 : jj == 2 ? c_pre2 : jj == 3 ? c_pre3
-                                                                                     : reinterpret_cast<float*>(C)[o];
-                        reinterpret_cast<float*>(C)[o] = old + v;
-                    } else {
-                        store_from_f32(C, c_dtype, o, v);
+                for (int u = 0; u < 4; ++u) {
+                    const bool live = j0 + u < j_end;                // the same for the whole warp
+                    const int m = m0 + j0 + u;
+                    float v = 0.0f;
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) v += x[u][r];
+                    if (epilogue == EPI_SWIGLU) {
+                        const float act = silu_mul_tc(v, __shfl_down_sync(0xffffffffu, v, 1));
+                        if (live && (lane & 1) == 0 && n + 1 < N) store_from_f32(C, c_dtype, (size_t)m * ldc + (n >> 1), act);
+                    } else if (live && n < N) {
+                        const size_t o = (size_t)m * ldc + n;
+                        if (epilogue == EPI_ACCUMULATE)
+                            reinterpret_cast<float*>(C)[o] = old[u] + v;
+                        else
+                            store_from_f32(C, c_dtype, o, v);
                     }
                 }
             }

@@ -1,15 +1,21 @@
 // Decode attention for bfloat16: one new token per sequence attends over its cached keys and
 // values (crates/bfi-core/src/cpu.rs:328-392 with T = 1).  The step is bound by reading the cache
 // once, so the work is split over (sequence, kv head, range of pages): each block streams its
-// pages of 64 keys through a two-stage cp.async ring in shared memory, all query heads of the
-// group share the loaded keys and values (they are the 16 rows of the tensor-core tiles), and
+// pages of 64 keys through a two-stage ring in shared memory -- one thread asks TMA for a page's
+// keys and values (boxes of 64 rows x 128 bytes, 128-byte swizzle: the layout ldmatrix reads
+// without bank conflicts), an mbarrier per stage says when they have landed -- all query heads of
+// the group share the loaded keys and values (they are the 16 rows of the tensor-core tiles), and
 // partial results (running maximum, sum and unnormalised output, float32) go to a scratch buffer.
 // They are merged in range order by a second kernel (which, launched as a programmatic dependent,
 // is already resident when the first one ends).
 //
 // Scores, the running maximum and sum, and the output accumulator are float32; exp is
 // ex2.approx on scores pre-multiplied by log2(e).
+//
+// Every wait on an mbarrier is bounded: a wait that runs out records BFI_STATUS_TIMEOUT in the
+// status word, the block gives its outstanding copies a bounded time to land and returns.
 #include "attention_tiles.cuh"
+#include "tcgen05.cuh"
 
 // A sequence's pages are cut into at most `max_splits` ranges of equal size (in pages), so every
 // sequence, long or short, spreads over the same number of blocks.
@@ -17,19 +23,38 @@ __device__ __forceinline__ int decode_pages_per_split(int n_pages, int max_split
     return (n_pages + max_splits - 1) / max_splits;
 }
 
+// A tile as TMA leaves it: D/64 boxes of [64 rows][64 values] one after the other, the 16-byte
+// chunk c of a box's row r at chunk c ^ (r & 7).  The tile starts on a 1024-byte boundary.
+template <int D>
+__device__ __forceinline__ bf16* box_chunk(bf16* tile, int row, int chunk) {
+    return tile + (chunk >> 3) * (AD_TILE * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
+}
+
+template <int D>
+struct DecodeSmem {
+    static constexpr int TILE_BYTES = AD_TILE * D * 2;            // keys or values of one page and kv head
+    static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    static constexpr int RING_BYTES = 2 * STAGE_BYTES;
+    static constexpr int MERGE_BYTES = AD_WARPS * 16 * (2 + D) * 4;
+    static constexpr int BODY_BYTES = RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES;
+    static constexpr size_t BYTES = (size_t)BODY_BYTES + 64 /*barriers*/ + 1024 /*alignment*/;
+};
+
 // part_o  [seqs, n_q, max_splits, D]  float32 unnormalised outputs
 // part_ml [seqs, n_q, max_splits, 2]  float32 (running max in log2 units, running sum)
 template <int D>
 __global__ void __launch_bounds__(AD_THREADS)
-attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out, long out_stride,
-                        const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                        const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out, long out_stride,
                         const int* __restrict__ block_table, int table_stride, const int* __restrict__ seq_slot,
                         const int* __restrict__ seq_start, int n_q, int n_kv, int window, float scale_log2,
-                        int head_chunks, float* __restrict__ part_o, float* __restrict__ part_ml) {
+                        int head_chunks, float* __restrict__ part_o, float* __restrict__ part_ml,
+                        int* __restrict__ status, uint32_t spin_limit) {
     pdl_trigger();
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    bf16* ks[2] = {reinterpret_cast<bf16*>(smem_raw), reinterpret_cast<bf16*>(smem_raw) + 2 * AD_TILE * D};
-    bf16* vs[2] = {ks[0] + AD_TILE * D, ks[1] + AD_TILE * D};
+    using Smem = DecodeSmem<D>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + Smem::BODY_BYTES);       // [2]
 
     const int seq = blockIdx.z;
     const int slot = seq_slot[seq];
@@ -52,30 +77,45 @@ attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
     if (split >= n_splits) return;
     const int p_beg = first_page + split * pages_per_split;
     const int p_end = min(last_page + 1, p_beg + pages_per_split);
+    const int n_tiles = p_end - p_beg;
 
-    const size_t page_elems = (size_t)n_kv * AD_TILE * D;
     const int* table = block_table + (size_t)slot * table_stride;
+    if (threadIdx.x == 0) {
+        mbar_init(&full[0], 1);
+        mbar_init(&full[1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
 
+    // thread 0 only: the keys and values of page `page_idx` of the sequence into stage `stage`
     auto issue = [&](int page_idx, int stage) {
         const int page = table[page_idx];
         if (page >= 0) {
-            const size_t base = (size_t)page * page_elems + (size_t)kvh * AD_TILE * D;
-            load_tile<D>(ks[stage], k_pages + base);
-            load_tile<D>(vs[stage], v_pages + base);
+            bf16* kt = reinterpret_cast<bf16*>(smem + (size_t)stage * Smem::STAGE_BYTES);
+            bf16* vt = kt + AD_TILE * D;
+            const int row = (page * n_kv + kvh) * AD_TILE;
+            mbar_expect_tx(&full[stage], Smem::STAGE_BYTES);
+#pragma unroll
+            for (int h = 0; h < D / 64; ++h) {
+                tma_load_2d(kt + h * (AD_TILE * 64), &map_k, h * 64, row, &full[stage]);
+                tma_load_2d(vt + h * (AD_TILE * 64), &map_v, h * 64, row, &full[stage]);
+            }
+        } else {
+            mbar_arrive(&full[stage]);                    // a page the sequence does not hold: nothing to wait for
         }
-        cp_async_commit();
     };
 
     // The sequence's older pages, its slot, position and page table were all written before this
     // step's kernels began; only the page of the new token (the last one) and q come from the
     // kernel before this one.  So the first two tiles, unless they are that page, travel before the wait.
-    int issued = 0;                                       // tiles on their way
-    while (issued < 2 && p_beg + issued < p_end && p_beg + issued != last_page) {
-        issue(p_beg + issued, issued);
-        ++issued;
-    }
+    int issued = 0;                                       // tiles on their way (thread 0 keeps count)
+    if (threadIdx.x == 0)
+        while (issued < 2 && issued < n_tiles && p_beg + issued != last_page) {
+            issue(p_beg + issued, issued);
+            ++issued;
+        }
     pdl_wait();
-    if (issued == 0 && p_beg < p_end) {
+    if (threadIdx.x == 0 && issued == 0 && n_tiles > 0) {
         issue(p_beg, 0);
         issued = 1;
     }
@@ -105,29 +145,28 @@ attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
 #pragma unroll
         for (int j = 0; j < 4; ++j) o[i][j] = 0.0f;
 
-    for (int p = p_beg; p < p_end; ++p) {
-        const int stage = (p - p_beg) & 1;
-        if (p + 1 < p_end) {
-            if (p + 1 - p_beg >= issued) {
-                issue(p + 1, stage ^ 1);
-                ++issued;
-            }
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
+    bool ok = true;
+    for (int it = 0; it < n_tiles; ++it) {
+        const int p = p_beg + it;
+        const int stage = it & 1;
+        // the other stage was read for the last time before the barrier that ended the iteration before
+        if (threadIdx.x == 0 && it + 1 < n_tiles && it + 1 >= issued) {
+            issue(p + 1, stage ^ 1);
+            ++issued;
         }
-        __syncthreads();
+        ok = __syncthreads_and(mbar_wait(&full[stage], (uint32_t)((it >> 1) & 1), spin_limit));
+        if (!ok) break;                                   // the same for every thread of the block
         const bool have_page = table[p] >= 0;
-        const bf16* kt = ks[stage];
-        const bf16* vt = vs[stage];
+        bf16* kt = reinterpret_cast<bf16*>(smem + (size_t)stage * Smem::STAGE_BYTES);
+        bf16* vt = kt + AD_TILE * D;
         if ((p + 1) * AD_TILE - 1 > pos) {
             // the page that holds `pos`: its later rows were never written.  Their scores are masked,
             // but a weight of zero times a stray NaN would still poison the output, so clear them.
             const int first_bad = pos - p * AD_TILE + 1;
             constexpr int CHUNKS = D / 8;
-            for (int i = threadIdx.x; i < (AD_TILE - first_bad) * CHUNKS; i += AD_THREADS) {
-                const int row = first_bad + i / CHUNKS, c = i % CHUNKS;
-                *reinterpret_cast<uint4*>(vs[stage] + row * D + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+            for (int i2 = threadIdx.x; i2 < (AD_TILE - first_bad) * CHUNKS; i2 += AD_THREADS) {
+                const int row = first_bad + i2 / CHUNKS, c = i2 % CHUNKS;
+                *reinterpret_cast<uint4*>(box_chunk<D>(vt, row, c)) = make_uint4(0u, 0u, 0u, 0u);
             }
             __syncthreads();
         }
@@ -137,7 +176,7 @@ attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) s[j][i] = 0.0f;
+            for (int i2 = 0; i2 < 4; ++i2) s[j][i2] = 0.0f;
 #pragma unroll
         for (int kk = 0; kk < D / 16; kk += 2) {
 #pragma unroll
@@ -145,7 +184,7 @@ attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
                 // four 8x8 matrices: key rows of n-tile j, chunks 2kk .. 2kk+3 (two k16 steps)
                 uint32_t b[4];
                 const int row = warp * 16 + j * 8 + (lane & 7);
-                ldmatrix_x4(b, tile_chunk<D>(kt, row, 2 * kk + (lane >> 3)));
+                ldmatrix_x4(b, box_chunk<D>(kt, row, 2 * kk + (lane >> 3)));
                 mma16816(s[j], qa[kk], b[0], b[1]);
                 mma16816(s[j], qa[kk + 1], b[2], b[3]);
             }
@@ -201,7 +240,7 @@ attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
             for (int dd = 0; dd < D / 8; dd += 2) {
                 uint32_t b[4];
                 const int row = warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
-                ldmatrix_x4_trans(b, tile_chunk<D>(vt, row, dd + (lane >> 4)));
+                ldmatrix_x4_trans(b, box_chunk<D>(vt, row, dd + (lane >> 4)));
                 mma16816(o[dd], pa, b[0], b[1]);
                 mma16816(o[dd + 1], pa, b[2], b[3]);
             }
@@ -209,8 +248,20 @@ attention_decode_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
         __syncthreads();      // the stage is free for the load issued in the next iteration
     }
 
+    if (!ok) {
+        // a wait ran out: say so, give the copies that were asked for a bounded time to land in
+        // this block's shared memory, and leave without a result
+        if (threadIdx.x == 0) {
+            atomicOr(status, BFI_STATUS_TIMEOUT);
+            for (int j = 0; j < issued; ++j)
+                if (j + 2 >= issued) mbar_wait(&full[j & 1], (uint32_t)((j >> 1) & 1), spin_limit);
+        }
+        __syncthreads();
+        return;
+    }
+
     // ---- merge the four warps (each saw a quarter of every tile) through shared memory
-    float* mm = reinterpret_cast<float*>(smem_raw);                 // [warps][16][2]
+    float* mm = reinterpret_cast<float*>(smem);                     // [warps][16][2]
     float* oo = mm + AD_WARPS * 16 * 2;                             // [warps][16][D]
     __syncthreads();
 #pragma unroll
@@ -299,14 +350,17 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
 
 template <int D>
 static int launch_decode(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
-                         const void* v_pages, const int* block_table, int table_stride, const int* seq_slot,
-                         const int* seq_start, int n_seqs, int n_q, int n_kv, int window, float scale, int max_splits,
-                         float* part_o, float* part_ml, cudaStream_t stream) {
+                         const void* v_pages, long n_pages, const int* block_table, int table_stride,
+                         const int* seq_slot, const int* seq_start, int n_seqs, int n_q, int n_kv, int window, float scale,
+                         int max_splits, float* part_o, float* part_ml, int* status, cudaStream_t stream) {
+    CUtensorMap mk, mv;
+    int rc = bfi_tensor_map_bf16(k_pages, n_pages * n_kv * AD_TILE, D, D, AD_TILE, &mk);
+    if (rc) return rc;
+    rc = bfi_tensor_map_bf16(v_pages, n_pages * n_kv * AD_TILE, D, D, AD_TILE, &mv);
+    if (rc) return rc;
     const int group = n_q / n_kv;
     const int head_chunks = (group + 15) / 16;
-    const size_t smem = (size_t)4 * AD_TILE * D * sizeof(bf16);
-    const size_t merge_smem = (size_t)AD_WARPS * 16 * (2 + D) * sizeof(float);
-    const size_t need = smem > merge_smem ? smem : merge_smem;
+    const size_t need = DecodeSmem<D>::BYTES;
     auto kernel = attention_decode_kernel<D>;
     if (need > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need);
@@ -315,10 +369,10 @@ static int launch_decode(const void* q, long q_stride, void* out, long out_strid
     }
     dim3 grid(max_splits, n_kv * head_chunks, n_seqs);
     const float scale_log2 = scale * 1.4426950408889634f;
-    bfi_launch(kernel, grid, dim3(AD_THREADS), need, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,
-               (const bf16*)k_pages, (const bf16*)v_pages, block_table, table_stride, seq_slot, seq_start, n_q, n_kv, window,
-               scale_log2, head_chunks, part_o, part_ml);
-    int rc = bfi_check_launch("attention_decode");
+    bfi_launch(kernel, grid, dim3(AD_THREADS), need, stream, mk, mv, (const bf16*)q, q_stride, (bf16*)out, out_stride,
+               block_table, table_stride, seq_slot, seq_start, n_q, n_kv, window, scale_log2, head_chunks, part_o, part_ml,
+               status, (uint32_t)TC_SPIN_LIMIT);
+    rc = bfi_check_launch("attention_decode");
     if (rc || max_splits == 1) return rc;
 #define BFI_MERGE(CAP)                                                                                                   \
     bfi_launch(attention_decode_merge_kernel<D, CAP>, dim3(n_q, n_seqs), dim3(D), 0, stream, (const float*)part_o,        \
@@ -330,26 +384,31 @@ static int launch_decode(const void* q, long q_stride, void* out, long out_strid
     return bfi_check_launch("attention_decode_merge");
 }
 
-// Returns 0 on success, 1 on error, 2 when the shape is not taken (nothing launched).
+// The cache pages are [n_pages, n_kv, 64, d], contiguous.  Returns 0 on success, 1 on error, 2 when the
+// shape is not taken (nothing launched): head sizes other than 64/128, or operands TMA cannot address.
 // Every sequence's pages are cut into at most `max_splits` (up to 32) ranges.  With max_splits > 1 the caller
-// gives part_o [n_seqs*n_q*max_splits*d] and part_ml [n_seqs*n_q*max_splits*2] floats.
+// gives part_o [n_seqs*n_q*max_splits*d] and part_ml [n_seqs*n_q*max_splits*2] floats.  `status` points at
+// an int, zero before the first call, that gets BFI_STATUS_TIMEOUT when a wait for a page ran out.
 extern "C" int bfi_attention_decode_bf16(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
-                                         const void* v_pages, const int* block_table, int table_stride,
+                                         const void* v_pages, long n_pages, const int* block_table, int table_stride,
                                          const int* seq_slot, const int* seq_start, int n_seqs, int n_q, int n_kv,
                                          int d, int window, float scale, int max_splits, float* part_o, float* part_ml,
-                                         cudaStream_t stream) {
+                                         int* status, cudaStream_t stream) {
     BFI_REQUIRE(n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_decode: %d query heads do not divide into %d kv heads",
                 n_q, n_kv);
     BFI_REQUIRE(window >= 0 && max_splits >= 1 && max_splits <= 32, "attention_decode: bad window or split count (1..32)");
+    BFI_REQUIRE(status != nullptr && n_pages > 0, "attention_decode: no status word or no pages");
     if (n_seqs <= 0) return 0;
     if (d != 64 && d != 128) return 2;
     if (q_stride % 8 != 0 || ((uintptr_t)q & 15) || n_seqs > 65535) return 2;
+    if (((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) || n_pages * n_kv * AD_TILE > 0x7fffffffL) return 2;
     if (max_splits > 1) BFI_REQUIRE(part_o && part_ml, "attention_decode: split runs need the scratch buffers");
     if (d == 64)
-        return launch_decode<64>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride, seq_slot,
-                                 seq_start, n_seqs, n_q, n_kv, window, scale, max_splits, part_o, part_ml, stream);
-    return launch_decode<128>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride, seq_slot,
-                              seq_start, n_seqs, n_q, n_kv, window, scale, max_splits, part_o, part_ml, stream);
+        return launch_decode<64>(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, table_stride,
+                                 seq_slot, seq_start, n_seqs, n_q, n_kv, window, scale, max_splits, part_o, part_ml, status,
+                                 stream);
+    return launch_decode<128>(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, table_stride, seq_slot,
+                              seq_start, n_seqs, n_q, n_kv, window, scale, max_splits, part_o, part_ml, status, stream);
 }
 
 BFI_TRACE_EXPORT(attention_decode)

@@ -170,6 +170,8 @@ def attention_decode_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads
     d = kv.head_dim
     if d not in (64, 128) or qkv.dtype != torch.bfloat16 or kv.k.dtype != torch.bfloat16:
         return False
+    if not kv.k.is_contiguous() or not kv.v.is_contiguous():
+        return False
     max_pages = kv.block_table.shape[1]
     bucket = getattr(ctx, "pages_bucket", 0)
     if bucket:
@@ -184,9 +186,9 @@ def attention_decode_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads
         part_ml = ctx.workspace.vector("attn.part_ml", ctx.n_seqs * n_heads * max_splits * 2, torch.float32)
     return library("fast").call_optional(
         "bfi_attention_decode_bf16", _ptr(qkv), c_long(qkv.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(kv.k),
-        _ptr(kv.v), _ptr(kv.block_table), c_int(kv.block_table.stride(0)), _ptr(ctx.seq_slot), _ptr(ctx.seq_start),
-        c_int(ctx.n_seqs), c_int(n_heads), c_int(kv.n_kv_heads), c_int(d), c_int(kv.window or 0), c_float(scale),
-        c_int(max_splits), _ptr(part_o), _ptr(part_ml), _stream())
+        _ptr(kv.v), c_long(kv.k.shape[0]), _ptr(kv.block_table), c_int(kv.block_table.stride(0)), _ptr(ctx.seq_slot),
+        _ptr(ctx.seq_start), c_int(ctx.n_seqs), c_int(n_heads), c_int(kv.n_kv_heads), c_int(d), c_int(kv.window or 0),
+        c_float(scale), c_int(max_splits), _ptr(part_o), _ptr(part_ml), _ptr(tc_status(qkv.device)), _stream())
 
 
 def attention_prefill_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float) -> bool:

@@ -49,8 +49,9 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         const int* __restrict__ block_table, int table_stride, const int* __restrict__ seq_slot,
                         const int* __restrict__ seq_start, int n_q, int n_kv, int window, float scale_log2,
                         int head_chunks, float* __restrict__ part_o, float* __restrict__ part_ml,
-                        int* __restrict__ status, uint32_t spin_limit) {
+                        int* __restrict__ status, TcWaits waits) {
     pdl_trigger();
+    const uint32_t spin_limit = waits.spin_limit;
     using Smem = DecodeSmem<D>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -109,13 +110,14 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     // step's kernels began; only the page of the new token (the last one) and q come from the
     // kernel before this one.  So the first two tiles, unless they are that page, travel before the wait.
     int issued = 0;                                       // tiles on their way (thread 0 keeps count)
-    if (threadIdx.x == 0)
+    const bool producer = threadIdx.x == 0 && !waits.hold_producer;
+    if (producer)
         while (issued < 2 && issued < n_tiles && p_beg + issued != last_page) {
             issue(p_beg + issued, issued);
             ++issued;
         }
     pdl_wait();
-    if (threadIdx.x == 0 && issued == 0 && n_tiles > 0) {
+    if (producer && issued == 0 && n_tiles > 0) {
         issue(p_beg, 0);
         issued = 1;
     }
@@ -150,7 +152,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         const int p = p_beg + it;
         const int stage = it & 1;
         // the other stage was read for the last time before the barrier that ended the iteration before
-        if (threadIdx.x == 0 && it + 1 < n_tiles && it + 1 >= issued) {
+        if (producer && it + 1 < n_tiles && it + 1 >= issued) {
             issue(p + 1, stage ^ 1);
             ++issued;
         }
@@ -352,7 +354,7 @@ template <int D>
 static int launch_decode(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
                          const void* v_pages, long n_pages, const int* block_table, int table_stride,
                          const int* seq_slot, const int* seq_start, int n_seqs, int n_q, int n_kv, int window, float scale,
-                         int max_splits, float* part_o, float* part_ml, int* status, cudaStream_t stream) {
+                         int max_splits, float* part_o, float* part_ml, int* status, cudaStream_t stream, TcWaits waits) {
     CUtensorMap mk, mv;
     int rc = bfi_tensor_map_bf16(k_pages, n_pages * n_kv * AD_TILE, D, D, AD_TILE, &mk);
     if (rc) return rc;
@@ -371,7 +373,7 @@ static int launch_decode(const void* q, long q_stride, void* out, long out_strid
     const float scale_log2 = scale * 1.4426950408889634f;
     bfi_launch(kernel, grid, dim3(AD_THREADS), need, stream, mk, mv, (const bf16*)q, q_stride, (bf16*)out, out_stride,
                block_table, table_stride, seq_slot, seq_start, n_q, n_kv, window, scale_log2, head_chunks, part_o, part_ml,
-               status, (uint32_t)TC_SPIN_LIMIT);
+               status, waits);
     rc = bfi_check_launch("attention_decode");
     if (rc || max_splits == 1) return rc;
 #define BFI_MERGE(CAP)                                                                                                   \
@@ -389,11 +391,11 @@ static int launch_decode(const void* q, long q_stride, void* out, long out_strid
 // Every sequence's pages are cut into at most `max_splits` (up to 32) ranges.  With max_splits > 1 the caller
 // gives part_o [n_seqs*n_q*max_splits*d] and part_ml [n_seqs*n_q*max_splits*2] floats.  `status` points at
 // an int, zero before the first call, that gets BFI_STATUS_TIMEOUT when a wait for a page ran out.
-extern "C" int bfi_attention_decode_bf16(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
-                                         const void* v_pages, long n_pages, const int* block_table, int table_stride,
-                                         const int* seq_slot, const int* seq_start, int n_seqs, int n_q, int n_kv,
-                                         int d, int window, float scale, int max_splits, float* part_o, float* part_ml,
-                                         int* status, cudaStream_t stream) {
+static int attention_decode_launch(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
+                                   const void* v_pages, long n_pages, const int* block_table, int table_stride,
+                                   const int* seq_slot, const int* seq_start, int n_seqs, int n_q, int n_kv, int d,
+                                   int window, float scale, int max_splits, float* part_o, float* part_ml, int* status,
+                                   cudaStream_t stream, TcWaits waits) {
     BFI_REQUIRE(n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_decode: %d query heads do not divide into %d kv heads",
                 n_q, n_kv);
     BFI_REQUIRE(window >= 0 && max_splits >= 1 && max_splits <= 32, "attention_decode: bad window or split count (1..32)");
@@ -406,9 +408,37 @@ extern "C" int bfi_attention_decode_bf16(const void* q, long q_stride, void* out
     if (d == 64)
         return launch_decode<64>(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, table_stride,
                                  seq_slot, seq_start, n_seqs, n_q, n_kv, window, scale, max_splits, part_o, part_ml, status,
-                                 stream);
+                                 stream, waits);
     return launch_decode<128>(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, table_stride, seq_slot,
-                              seq_start, n_seqs, n_q, n_kv, window, scale, max_splits, part_o, part_ml, status, stream);
+                              seq_start, n_seqs, n_q, n_kv, window, scale, max_splits, part_o, part_ml, status, stream,
+                              waits);
+}
+
+extern "C" int bfi_attention_decode_bf16(const void* q, long q_stride, void* out, long out_stride, const void* k_pages,
+                                         const void* v_pages, long n_pages, const int* block_table, int table_stride,
+                                         const int* seq_slot, const int* seq_start, int n_seqs, int n_q, int n_kv,
+                                         int d, int window, float scale, int max_splits, float* part_o, float* part_ml,
+                                         int* status, cudaStream_t stream) {
+    return attention_decode_launch(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, table_stride,
+                                   seq_slot, seq_start, n_seqs, n_q, n_kv, d, window, scale, max_splits, part_o, part_ml,
+                                   status, stream, tc_waits_default());
+}
+
+// The same launch with its bounded waits cut to `spin_limit` polls and, with hold_producer, a thread
+// that asks for no page at all: every wait for a page then runs out by construction.  The launch
+// records BFI_STATUS_TIMEOUT in the status word, writes no output and returns; nothing faults and
+// nothing waits without a bound.  For the tests of that path only.
+extern "C" int bfi_attention_decode_bf16_wait_probe(const void* q, long q_stride, void* out, long out_stride,
+                                                    const void* k_pages, const void* v_pages, long n_pages,
+                                                    const int* block_table, int table_stride, const int* seq_slot,
+                                                    const int* seq_start, int n_seqs, int n_q, int n_kv, int d,
+                                                    int window, float scale, int max_splits, float* part_o,
+                                                    float* part_ml, int* status, unsigned spin_limit, int hold_producer,
+                                                    cudaStream_t stream) {
+    BFI_REQUIRE(spin_limit > 0 && spin_limit <= TC_SPIN_LIMIT, "attention_decode probe: spin limit out of range");
+    return attention_decode_launch(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, table_stride,
+                                   seq_slot, seq_start, n_seqs, n_q, n_kv, d, window, scale, max_splits, part_o, part_ml,
+                                   status, stream, TcWaits{spin_limit, hold_producer ? 1 : 0});
 }
 
 BFI_TRACE_EXPORT(attention_decode)

@@ -166,7 +166,11 @@ def decode_splits(n_seqs: int, n_kv: int, group: int, max_pages: int, n_sm: int)
     return max(1, min(max(fill, length), max_pages, 32))
 
 
-def attention_decode_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float) -> bool:
+def attention_decode_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float,
+                          probe=None) -> bool:
+    """One new token per sequence over its cached pages, which arrive by TMA: the cache must be
+    contiguous.  A wait for a page that ran out shows in ``tc_status``.  ``probe``: (polls, hold
+    the producer), for ``attention_decode_wait_probe``."""
     d = kv.head_dim
     if d not in (64, 128) or qkv.dtype != torch.bfloat16 or kv.k.dtype != torch.bfloat16:
         return False
@@ -184,11 +188,21 @@ def attention_decode_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads
     if max_splits > 1:
         part_o = ctx.workspace.vector("attn.part_o", ctx.n_seqs * n_heads * max_splits * d, torch.float32)
         part_ml = ctx.workspace.vector("attn.part_ml", ctx.n_seqs * n_heads * max_splits * 2, torch.float32)
-    return library("fast").call_optional(
-        "bfi_attention_decode_bf16", _ptr(qkv), c_long(qkv.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(kv.k),
-        _ptr(kv.v), c_long(kv.k.shape[0]), _ptr(kv.block_table), c_int(kv.block_table.stride(0)), _ptr(ctx.seq_slot),
-        _ptr(ctx.seq_start), c_int(ctx.n_seqs), c_int(n_heads), c_int(kv.n_kv_heads), c_int(d), c_int(kv.window or 0),
-        c_float(scale), c_int(max_splits), _ptr(part_o), _ptr(part_ml), _ptr(tc_status(qkv.device)), _stream())
+    args = [_ptr(qkv), c_long(qkv.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(kv.k), _ptr(kv.v),
+            c_long(kv.k.shape[0]), _ptr(kv.block_table), c_int(kv.block_table.stride(0)), _ptr(ctx.seq_slot),
+            _ptr(ctx.seq_start), c_int(ctx.n_seqs), c_int(n_heads), c_int(kv.n_kv_heads), c_int(d), c_int(kv.window or 0),
+            c_float(scale), c_int(max_splits), _ptr(part_o), _ptr(part_ml), _ptr(tc_status(qkv.device))]
+    if probe is None:
+        return library("fast").call_optional("bfi_attention_decode_bf16", *args, _stream())
+    return library("fast").call_optional("bfi_attention_decode_bf16_wait_probe", *args, c_int(int(probe[0])),
+                                         c_int(1 if probe[1] else 0), _stream())
+
+
+def attention_decode_wait_probe(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float,
+                                spin_limit: int, hold_producer: bool) -> bool:
+    """The decode attention with its bounded waits cut to ``spin_limit`` polls and, if asked, a
+    thread that asks for no page: see ``gemm_tcgen05_wait_probe``."""
+    return attention_decode_bf16(ctx, qkv, out, kv, n_heads, scale, probe=(spin_limit, hold_producer))
 
 
 def attention_prefill_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float) -> bool:

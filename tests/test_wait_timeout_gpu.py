@@ -22,6 +22,8 @@ POLLS = 2000
 
 
 def timed(fn):
+    from builderforce_inference_b200.kernels.library import library
+    library("fast")                                   # built and loaded before the clock starts
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     assert fn()
@@ -73,6 +75,48 @@ def test_prompt_attention_wait_runs_out_and_the_next_launch_is_right(d):
     ref = plain_paged_attention(q, k, v, 0, None, scale).reshape(n, n_q * d)
     for _ in range(2):
         assert fast().attention_prefill_tcgen05_bf16(ctx, q_dev, out, pages.view, n_q, scale)
+        torch.cuda.synchronize()
+        assert tc_status_clear() == 0
+        assert rel_err(out.float().cpu(), ref) < 1e-2
+
+
+@pytest.mark.parametrize("d,forced", [(64, 1), (128, 1), (128, 4)])
+def test_decode_attention_wait_runs_out_and_the_next_launch_is_right(d, forced, monkeypatch):
+    """The pages of the decode attention come by TMA onto an mbarrier per stage: with a thread that
+    asks for no page every block's first wait runs out."""
+    from test_fast_kernels_gpu import Ctx
+    n_q, n_kv = 8, 2
+    starts = [5, 130, 700]
+    assert tc_status_clear() == 0
+    g = gen(d + forced)
+    scale = 1.0 / math.sqrt(d)
+    pages = Pages(len(starts), 768, n_kv, d, torch.bfloat16, seed=4)
+    qs, refs = [], []
+    for slot, start in enumerate(starts):
+        n = start + 1
+        k = torch.randn(n, n_kv, d, generator=g).bfloat16().float()
+        v = torch.randn(n, n_kv, d, generator=g).bfloat16().float()
+        q = torch.randn(1, n_q, d, generator=g).bfloat16().float()
+        pages.write(slot, 0, k, v)
+        qs.append(q.reshape(1, n_q * d))
+        refs.append(plain_paged_attention(q, k, v, start, None, scale).reshape(1, n_q * d))
+    q_all, ref = torch.cat(qs).bfloat16().to(DEV), torch.cat(refs)
+    monkeypatch.setattr(fast(), "decode_splits", lambda *a: forced)
+    ctx = Ctx(list(range(len(starts))), starts)
+    out = torch.full((len(starts), n_q * d), 7.0, dtype=torch.bfloat16, device=DEV)
+    took = timed(lambda: fast().attention_decode_wait_probe(ctx, q_all, out, pages.view, n_q, scale, POLLS, True))
+    assert took < 2.0, f"the launch took {took:.2f} s to give up"
+    assert tc_status_clear() & TIMEOUT_BIT
+    if forced == 1:                                   # no second kernel: nothing was written
+        assert float(out.float().min()) == 7.0 and float(out.float().max()) == 7.0
+    # a short limit alone, with the pages asked for, trips nothing
+    assert fast().attention_decode_wait_probe(ctx, q_all, out, pages.view, n_q, scale, 65536, False)
+    torch.cuda.synchronize()
+    assert tc_status_clear() == 0
+    assert rel_err(out.float().cpu(), ref) < 1e-2
+    for _ in range(2):
+        out.fill_(7.0)
+        assert fast().attention_decode_bf16(ctx, q_all, out, pages.view, n_q, scale)
         torch.cuda.synchronize()
         assert tc_status_clear() == 0
         assert rel_err(out.float().cpu(), ref) < 1e-2

@@ -313,13 +313,30 @@ def kernel_run(a) -> int:
     ``--kernel skinny_gemm|gemm_tcgen05 --shape qkv|o|gateup|down|head --rows M`` or
     ``--kernel attention_decode|attention_prefill|attention_prefill_tcgen05 --rows B_or_T --ctx C``
     (``--seqs N``: N prompts of --rows tokens each),
-    ``--kernel qk_norm_rope --rows T``.  Weights rotate over
-    enough copies to exceed L2.  Prints one JSON line."""
+    ``--kernel qk_norm_rope --rows T``, ``--kernel weight_stream --shape S [--stages R] [--ksplit Z]`` (the
+    matrix read once through the few-row products' TMA rings and nothing else: the floor under
+    them).  Weights rotate over enough copies to exceed L2.  Prints one JSON line."""
     import torch
     from builderforce_inference_b200.kernels import fast_ops
     dev = torch.device("cuda:0")
     reps = a.steps
-    if a.kernel in ("skinny_gemm", "gemm_tcgen05"):
+    if a.kernel == "weight_stream":
+        # the floor under the few-row products: the matrix read once through their TMA rings, nothing else
+        n, k, _ = KERNEL_SHAPES[a.shape]
+        copies = max(2, int(400e6 // (n * k * 2)) + 1)
+        ws = [torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+
+        stages = a.stages
+        # K split as the few-row product plans it: enough blocks for two per SM, at least 8 k blocks each
+        tiles, kblocks, n_sm = (n + 127) // 128, (k + 63) // 64, fast_ops.sm_count(dev)
+        ksplit = a.ksplit or (max(1, min(8, 2 * n_sm // tiles, kblocks // 8)) if tiles * 2 <= 2 * n_sm else 1)
+
+        def one(i):
+            if not fast_ops.weight_stream(ws[i % copies], stages=stages, ksplit=ksplit):
+                raise SystemExit("weight_stream does not take this matrix")
+        bytes_moved, flops = n * k * 2, 0.0
+        what = {"shape": a.shape, "N": n, "K": k, "stages": stages, "ksplit": ksplit}
+    elif a.kernel in ("skinny_gemm", "gemm_tcgen05"):
         n, k, epi = KERNEL_SHAPES[a.shape]
         m = a.rows
         copies = max(2, int(400e6 // (n * k * 2)) + 1)
@@ -526,11 +543,13 @@ def main() -> int:
     ap.add_argument("--timeline-layer", type=int, default=6)
     ap.add_argument("--timeline-prompt", type=int, default=0, help="with --timeline: a prompt step of this many tokens instead")
     ap.add_argument("--seqs", type=int, default=1, help="kernel mode, prompt attention: prompts of --rows tokens each")
-    ap.add_argument("--kernel", default=None, choices=["skinny_gemm", "gemm_tcgen05", "qk_norm_rope", "attention_decode",
+    ap.add_argument("--kernel", default=None, choices=["skinny_gemm", "gemm_tcgen05", "weight_stream", "qk_norm_rope", "attention_decode",
                                                        "attention_prefill", "attention_prefill_tcgen05"],
                     help="time one kernel instead of the model (see kernel_run)")
     ap.add_argument("--shape", default="qkv", choices=sorted(KERNEL_SHAPES))
     ap.add_argument("--eager", action="store_true", help="with --kernel: plain launches instead of one CUDA graph")
+    ap.add_argument("--stages", type=int, default=6, help="--kernel weight_stream: 16 KB tiles in a block's ring (1..12)")
+    ap.add_argument("--ksplit", type=int, default=0, help="--kernel weight_stream: ranges of K (0: as the product plans it)")
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=2048)
     ap.add_argument("--gpus", type=int, default=1)

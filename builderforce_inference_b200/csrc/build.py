@@ -26,7 +26,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIBRARIES: Dict[str, List[str]] = {
     "core": ["errors.cu", "elementwise.cu", "gemm_simt.cu", "attention_paged.cu", "sampling.cu", "utility.cu"],
     "fast": ["errors.cu", "skinny_gemm.cu", "attention_decode.cu", "attention_prefill.cu", "gemm_tcgen05.cu",
-             "attention_prefill_tcgen05.cu"],
+             "attention_prefill_tcgen05.cu", "weight_stream.cu"],
 }
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]

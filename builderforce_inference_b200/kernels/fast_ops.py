@@ -140,6 +140,22 @@ def gemm_tcgen05_wait_probe(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
         _ptr(tc_status(a.device)), c_int(int(spin_limit)), c_int(1 if hold_producer else 0), _stream())
 
 
+_stream_sinks = {}
+
+
+def weight_stream(w: torch.Tensor, stages: int = 6, ksplit: int = 1) -> bool:
+    """Reads ``w`` once through the few-row products' TMA rings and does nothing with it: the time
+    of this launch is the floor under a product of that shape (see ``csrc/weight_stream.cu``)."""
+    if w.dtype != torch.bfloat16 or w.dim() != 2 or w.stride(1) != 1:
+        raise KernelError("weight_stream wants a bfloat16 matrix with unit column stride")
+    sink = _stream_sinks.get(w.device)
+    if sink is None:
+        sink = _stream_sinks[w.device] = torch.zeros(1, dtype=torch.int64, device=w.device)
+    return library("fast").call_optional("bfi_weight_stream_bf16", _ptr(w), c_long(w.stride(0)), c_int(w.shape[0]),
+                                         c_int(w.shape[1]), c_int(stages), c_int(ksplit), _ptr(tc_status(w.device)),
+                                         _ptr(sink), _stream())
+
+
 def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int) -> bool:
     """bfloat16 x bfloat16 -> ``out`` (float32 or bfloat16): the tcgen05 kernel, whose blocks start
     streaming W into their shared memory while the kernel before them still runs; the register-fed

@@ -7,6 +7,7 @@ import torch
 
 from helpers import rel_err
 from plain import qwen3_plain as P
+from builderforce_inference_b200.kernels.library import KernelError
 from test_kernels_gpu import DEV, Pages, gen, plain_paged_attention
 
 pytestmark = pytest.mark.gpu
@@ -63,6 +64,20 @@ def test_skinny_gemm_declines_what_it_cannot_do():
     out = torch.empty(70, 9, dtype=torch.float32, device=DEV)
     linear(a, w, out)                                                  # K = 20: only the general kernel takes it
     assert rel_err(out, a.float().cpu() @ w.float().cpu().t()) < 2e-5
+
+
+@pytest.mark.parametrize("n,k,stages,ksplit", [(256, 512, 2, 1), (300, 1000, 6, 3), (128, 64, 12, 1)])
+def test_weight_stream_reads_a_matrix_and_trips_no_wait(n, k, stages, ksplit):
+    """The measuring kernel of the few-row products' rings: it computes nothing, so what there is
+    to check is that every size runs through and no bounded wait runs out."""
+    assert tc_status_clear() == 0
+    w = torch.randn(n, k, generator=gen(n)).bfloat16().to(DEV)
+    for _ in range(3):
+        assert fast().weight_stream(w, stages=stages, ksplit=ksplit)
+    torch.cuda.synchronize()
+    assert tc_status_clear() == 0
+    with pytest.raises(KernelError):
+        fast().weight_stream(w.float())
 
 
 class Ctx:

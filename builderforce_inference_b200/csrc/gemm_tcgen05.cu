@@ -10,7 +10,8 @@
 //   warp 0     one lane issues the TMA loads of W and A tiles (128-byte swizzle) into the ring
 //   warp 1     allocates tensor memory; one lane issues tcgen05.mma (4 per 64-wide k block) and
 //              commits each block to the ring's "empty" barrier, the last one to "tmem_full"
-//   warps 2-5  epilogue: tcgen05.ld of their 32 lanes, then store / add into the float32 residual /
+//   warps 2-5  epilogue (2-9 in the many-row kernel, two per quarter of the lanes): tcgen05.ld of
+//              their 32 lanes, then store / add into the float32 residual /
 //              SiLU(gate)*up over interleaved rows.  With K split, the blocks of one tile form a
 //              thread-block cluster: each leaves its partial tile in its own shared memory and
 //              then adds, in split order, a share of the tile's tokens out of all the blocks'
@@ -331,10 +332,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #define TP_RING_BYTES (4 * (TP_TOKENS + TP_FEATS) * TC_BK * 2)   // 192 KB
 #define TP_MAX_STAGES 8
 #define TP_SMEM ((size_t)TP_RING_BYTES + 1024 + 256)
+#define TP_EPI_WARPS 8                                           // two per quarter of the TMEM lanes: each takes half a tile's features
+#define TP_THREADS (64 + 32 * TP_EPI_WARPS)
 
 
 template <int HALVES>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TP_THREADS, 1)
 gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                             void* __restrict__ C, int c_dtype, long ldc, int M, int N, int K, int tiles_m, int tiles_n,
                             int tile_n, int n_stages, int epilogue, int vec_ok, int* __restrict__ status, TcWaits waits) {
@@ -361,7 +364,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&tmem_full[a], 1);
-            mbar_init(&tmem_empty[a], 4);          // one arrival per epilogue warp
+            mbar_init(&tmem_empty[a], TP_EPI_WARPS);   // one arrival per epilogue warp
         }
         s_flag[0] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -497,8 +500,12 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             const int acc = HALVES == 1 ? (local & 1) : h;
             const int m = tm * TILE_TOKENS + h * TP_TOKENS + quad * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * TP_FEATS;
+            // the two warps of a lane quarter share a token's features: chunks of 16, the first half and the second
+            const int n_chunks = tile_n / 16;
+            const int c_beg = (warp - 2) < 4 ? 0 : (n_chunks + 1) / 2;
+            const int c_end = (warp - 2) < 4 ? (n_chunks + 1) / 2 : n_chunks;
 #pragma unroll 1
-            for (int c = 0; c < tile_n / 16; ++c) {
+            for (int c = c_beg; c < c_end; ++c) {
                 const int n = tn * tile_n + c * 16;
                 if (n >= N) break;
                 float v[16];
@@ -803,10 +810,10 @@ static int launch_tc_prefill(const void* A, long lda, const void* W, long ldw, v
     const int elem = dtype_size(c_dtype);
     const int vec_ok = ((ldc * elem) % 16 == 0 && ((uintptr_t)C & 15) == 0) ? 1 : 0;
     if (halves == 2)
-        bfi_launch(gemm_tcgen05_prefill_kernel<2>, dim3(grid), dim3(TC_THREADS), TP_SMEM, stream, ma, mw, C, c_dtype, ldc, M, N,
+        bfi_launch(gemm_tcgen05_prefill_kernel<2>, dim3(grid), dim3(TP_THREADS), TP_SMEM, stream, ma, mw, C, c_dtype, ldc, M, N,
                    K, tiles_m, tiles_n, tile_n, n_stages, epilogue, vec_ok, status, waits);
     else
-        bfi_launch(gemm_tcgen05_prefill_kernel<1>, dim3(grid), dim3(TC_THREADS), TP_SMEM, stream, ma, mw, C, c_dtype, ldc, M, N,
+        bfi_launch(gemm_tcgen05_prefill_kernel<1>, dim3(grid), dim3(TP_THREADS), TP_SMEM, stream, ma, mw, C, c_dtype, ldc, M, N,
                    K, tiles_m, tiles_n, tile_n, n_stages, epilogue, vec_ok, status, waits);
     return bfi_check_launch("gemm_tcgen05_prefill");
 }

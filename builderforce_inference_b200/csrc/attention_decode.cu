@@ -30,12 +30,14 @@ __device__ __forceinline__ bf16* box_chunk(bf16* tile, int row, int chunk) {
     return tile + (chunk >> 3) * (AD_TILE * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
 }
 
+#define AD_MERGE_PAD 8
+
 template <int D>
 struct DecodeSmem {
     static constexpr int TILE_BYTES = AD_TILE * D * 2;            // keys or values of one page and kv head
     static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
     static constexpr int RING_BYTES = 2 * STAGE_BYTES;
-    static constexpr int MERGE_BYTES = AD_WARPS * 16 * (2 + D) * 4;
+    static constexpr int MERGE_BYTES = AD_WARPS * 16 * (2 + D + AD_MERGE_PAD) * 4;
     static constexpr int BODY_BYTES = RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES;
     static constexpr size_t BYTES = (size_t)BODY_BYTES + 64 /*barriers*/ + 1024 /*alignment*/;
 };
@@ -174,11 +176,13 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         }
 
         // ---- scores of this warp's 16 keys: two n-tiles of 8 keys
-        float s[2][4];
+        // two accumulators per n-tile (even and odd k steps), added at the end: the chain of
+        // dependent tensor-core instructions is half as long
+        float s[2][4], s_odd[2][4];
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
-            for (int i2 = 0; i2 < 4; ++i2) s[j][i2] = 0.0f;
+            for (int i2 = 0; i2 < 4; ++i2) s[j][i2] = s_odd[j][i2] = 0.0f;
 #pragma unroll
         for (int kk = 0; kk < D / 16; kk += 2) {
 #pragma unroll
@@ -188,9 +192,13 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 const int row = warp * 16 + j * 8 + (lane & 7);
                 ldmatrix_x4(b, box_chunk<D>(kt, row, 2 * kk + (lane >> 3)));
                 mma16816(s[j], qa[kk], b[0], b[1]);
-                mma16816(s[j], qa[kk + 1], b[2], b[3]);
+                mma16816(s_odd[j], qa[kk + 1], b[2], b[3]);
             }
         }
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int i2 = 0; i2 < 4; ++i2) s[j][i2] += s_odd[j][i2];
         // ---- mask and online softmax; c0,c1 -> row g, keys 2t,2t+1; c2,c3 -> row g+8
         const int key0 = p * AD_TILE + warp * 16;
         float p_frag[2][4];
@@ -262,21 +270,23 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         return;
     }
 
-    // ---- merge the four warps (each saw a quarter of every tile) through shared memory
+    // ---- merge the four warps (each saw a quarter of every tile) through shared memory: only the
+    // rows of heads that exist, rows AD_MERGE_PAD floats apart so that the lanes' pairs fall into distinct banks
+    constexpr int LD = D + AD_MERGE_PAD;
     float* mm = reinterpret_cast<float*>(smem);                     // [warps][16][2]
-    float* oo = mm + AD_WARPS * 16 * 2;                             // [warps][16][D]
+    float* oo = mm + AD_WARPS * 16 * 2;                             // [warps][16][LD]
     __syncthreads();
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = g + r * 8;
-        if (t == 0) {
-            mm[(warp * 16 + row) * 2] = m_run[r];
-            mm[(warp * 16 + row) * 2 + 1] = l_run[r];
-        }
+        if (row < n_heads) {
+            if (t == 0) {
+                mm[(warp * 16 + row) * 2] = m_run[r];
+                mm[(warp * 16 + row) * 2 + 1] = l_run[r];
+            }
 #pragma unroll
-        for (int i = 0; i < D / 8; ++i) {
-            oo[(size_t)(warp * 16 + row) * D + i * 8 + 2 * t] = o[i][r * 2];
-            oo[(size_t)(warp * 16 + row) * D + i * 8 + 2 * t + 1] = o[i][r * 2 + 1];
+            for (int i = 0; i < D / 8; ++i)
+                *reinterpret_cast<float2*>(oo + (size_t)(warp * 16 + row) * LD + i * 8 + 2 * t) = make_float2(o[i][r * 2], o[i][r * 2 + 1]);
         }
     }
     __syncthreads();
@@ -291,7 +301,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             const float mw = mm[(w * 16 + row) * 2];
             const float f = (mw == -INFINITY) ? 0.0f : fast_exp2(mw - m);
             l += mm[(w * 16 + row) * 2 + 1] * f;
-            acc += oo[(size_t)(w * 16 + row) * D + e] * f;
+            acc += oo[(size_t)(w * 16 + row) * LD + e] * f;
         }
         const int head = head0 + row;
         if (n_splits == 1) {

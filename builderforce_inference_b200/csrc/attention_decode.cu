@@ -204,6 +204,10 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         float p_frag[2][4];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
+            if (r == 1 && n_heads <= 8) {                 // rows 8..15 are heads this block does not have
+                p_frag[0][2] = p_frag[0][3] = p_frag[1][2] = p_frag[1][3] = 0.0f;
+                continue;
+            }
             float mx = -INFINITY;
 #pragma unroll
             for (int j = 0; j < 2; ++j)

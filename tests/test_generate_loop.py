@@ -228,6 +228,25 @@ def test_page_buckets_of_single_token_steps():
     assert pages_bucket(3, 2) == 4 and pages_bucket(1, 1) == 1
 
 
+def test_page_ranges_of_the_decode_attention():
+    """Into how many page ranges a step's sequences are cut: never more than a sequence can have
+    pages or the merge kernel takes (32), enough blocks to fill the SMs when the pages allow it, and
+    no range much longer than 24 pages unless the cap of 32 forces it."""
+    from builderforce_inference_b200.kernels.fast_ops import DECODE_PAGES_PER_BLOCK, decode_splits
+    for n_sm in (148, 132, 16):
+        for n_seqs in (1, 2, 8, 33, 64, 256):
+            for n_kv, group in ((8, 4), (1, 16), (2, 20), (4, 1)):
+                for max_pages in (1, 2, 4, 16, 64, 512, 2048):
+                    s = decode_splits(n_seqs, n_kv, group, max_pages, n_sm)
+                    assert 1 <= s <= min(32, max_pages)
+                    blocks = n_seqs * n_kv * ((group + 15) // 16)
+                    if s < min(32, max_pages):          # not at a cap: the GPU is filled and ranges are short
+                        assert blocks * s >= 2 * n_sm
+                        assert -(-max_pages // s) <= DECODE_PAGES_PER_BLOCK
+    assert decode_splits(8, 8, 4, 64, 148) == 6 and decode_splits(64, 8, 4, 64, 148) == 3
+    assert decode_splits(1, 8, 4, 64, 148) == 32 and decode_splits(64, 8, 4, 16, 148) == 1
+
+
 class AheadToyStepper(ToyStepper):
     """The toy stepper with the one-step-ahead interface: a ticket is the list of ids "on the
     device"; the loop may read it only through ``sample_wait``."""

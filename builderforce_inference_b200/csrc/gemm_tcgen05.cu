@@ -331,9 +331,111 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #define TP_FEATS 256                                             // widest tile; the accumulators' stride
 #define TP_RING_BYTES (4 * (TP_TOKENS + TP_FEATS) * TC_BK * 2)   // 192 KB
 #define TP_MAX_STAGES 8
-#define TP_SMEM ((size_t)TP_RING_BYTES + 1024 + 256)
 #define TP_EPI_WARPS 8                                           // two per quarter of the TMEM lanes: each takes half a tile's features
 #define TP_THREADS (64 + 32 * TP_EPI_WARPS)
+#define TP_STAGE_BYTES 4096                                      // per epilogue warp: 32 token rows of 128 bytes on their way out
+#define TP_SMEM ((size_t)TP_RING_BYTES + 1024 + 256 + TP_EPI_WARPS * TP_STAGE_BYTES)
+
+// A group of G chunks (16 features each) of an epilogue warp's 32 tokens, out through shared memory.
+// After tcgen05.ld a lane holds ONE token's values, so a store straight from the registers touches 32
+// different lines with a few bytes each; here each lane leaves its token's row (up to 128 bytes, as
+// 16-byte pieces, piece j at position j ^ (row & 7): no bank conflicts either way) in the warp's
+// staging tile, and the warp then writes (or, adding, reads and writes) whole rows: 8 lanes a row.
+// G = 2 for float32 outputs, 4 for bfloat16 and for the gated epilogue.
+template <int G>
+__device__ __forceinline__ void tp_emit_group(uint4* stage, const float (&v)[G][16], int lane, int epilogue, int c_dtype,
+                                              void* __restrict__ C, long ldc, int m_base, int M, int n0) {
+    uint4 piece[8];
+    int n_pieces;
+    size_t out_byte0;                     // of the group's first output in its row of C
+    if (epilogue == EPI_SWIGLU) {
+        if (c_dtype == BFI_BF16) {        // 16 features -> 8 outputs -> one piece per chunk
+            n_pieces = G;
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                uint32_t pk[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    __nv_bfloat162 t2 = __floats2bfloat162_rn(silu_mul_tc(v[g][4 * j], v[g][4 * j + 1]),
+                                                              silu_mul_tc(v[g][4 * j + 2], v[g][4 * j + 3]));
+                    pk[j] = *reinterpret_cast<uint32_t*>(&t2);
+                }
+                piece[g] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+            out_byte0 = (size_t)(n0 >> 1) * 2;
+        } else {                          // float32: two pieces per chunk
+            n_pieces = 2 * G;
+#pragma unroll
+            for (int g = 0; g < G; ++g)
+#pragma unroll
+                for (int q = 0; q < 2; ++q)
+                    piece[(2 * g + q) & 7] = make_uint4(__float_as_uint(silu_mul_tc(v[g][8 * q], v[g][8 * q + 1])),
+                                                        __float_as_uint(silu_mul_tc(v[g][8 * q + 2], v[g][8 * q + 3])),
+                                                        __float_as_uint(silu_mul_tc(v[g][8 * q + 4], v[g][8 * q + 5])),
+                                                        __float_as_uint(silu_mul_tc(v[g][8 * q + 6], v[g][8 * q + 7])));
+            out_byte0 = (size_t)(n0 >> 1) * 4;
+        }
+    } else if (c_dtype == BFI_BF16) {     // two pieces per chunk
+        n_pieces = 2 * G;
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                uint32_t pk[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    __nv_bfloat162 t2 = __floats2bfloat162_rn(v[g][8 * q + 2 * j], v[g][8 * q + 2 * j + 1]);
+                    pk[j] = *reinterpret_cast<uint32_t*>(&t2);
+                }
+                piece[(2 * g + q) & 7] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+        out_byte0 = (size_t)n0 * 2;
+    } else {                              // float32, stored or added: four pieces per chunk (G = 2)
+        n_pieces = 4 * G;
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                piece[(4 * g + q) & 7] = make_uint4(__float_as_uint(v[g][4 * q]), __float_as_uint(v[g][4 * q + 1]),
+                                                    __float_as_uint(v[g][4 * q + 2]), __float_as_uint(v[g][4 * q + 3]));
+        out_byte0 = (size_t)n0 * 4;
+    }
+    __syncwarp();                         // the tile is free: every lane has read what the group before left
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        if (j < n_pieces) stage[lane * 8 + (j ^ (lane & 7))] = piece[j];
+    __syncwarp();
+    const size_t row_bytes = (size_t)ldc * (c_dtype == BFI_F32 ? 4 : 2);
+    const int shift = n_pieces == 8 ? 3 : (n_pieces == 4 ? 2 : 1);       // rows per pass: 32 >> shift lanes... pieces a row = 1 << shift
+    unsigned char* c_bytes = reinterpret_cast<unsigned char*>(C);
+    if (epilogue == EPI_ACCUMULATE) {
+        float4 old[8];
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int idx = it * 32 + lane, row = idx >> 3, j = idx & 7;
+            old[it] = m_base + row < M ? __ldcg(reinterpret_cast<const float4*>(c_bytes + (size_t)(m_base + row) * row_bytes + out_byte0 + j * 16))
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int idx = it * 32 + lane, row = idx >> 3, j = idx & 7;
+            const uint4 add = stage[row * 8 + (j ^ (row & 7))];
+            if (m_base + row < M)
+                *reinterpret_cast<float4*>(c_bytes + (size_t)(m_base + row) * row_bytes + out_byte0 + j * 16) =
+                    make_float4(old[it].x + __uint_as_float(add.x), old[it].y + __uint_as_float(add.y),
+                                old[it].z + __uint_as_float(add.z), old[it].w + __uint_as_float(add.w));
+        }
+    } else {
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            if (it >= n_pieces) break;
+            const int idx = it * 32 + lane, row = idx >> shift, j = idx & (n_pieces - 1);
+            if (m_base + row < M)
+                *reinterpret_cast<uint4*>(c_bytes + (size_t)(m_base + row) * row_bytes + out_byte0 + j * 16) =
+                    stage[row * 8 + (j ^ (row & 7))];
+        }
+    }
+}
 
 
 template <int HALVES>
@@ -488,6 +590,20 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             tile_coords(tile, tm, tn);
             const int full_idx = HALVES == 1 ? (local & 1) : 0;
             const uint32_t full_parity = HALVES == 1 ? (uint32_t)((local >> 1) & 1) : (uint32_t)(local & 1);
+            if (epilogue == EPI_ACCUMULATE) {
+                // the sums this tile will be added to are asked into L2 now, while its products run:
+                // in a step the residual has long left L2 when a product comes to add into it
+                const int n_first = tn * tile_n;
+                const int n_feats = min(tile_n, N - n_first);
+                for (int h = 0; h < HALVES; ++h) {
+                    const int mm = tm * TILE_TOKENS + h * TP_TOKENS + quad * 32 + lane;
+                    if (mm < M) {
+                        const char* row = reinterpret_cast<const char*>(C) + ((size_t)mm * ldc + n_first) * 4;
+                        for (int off = (warp - 2 < 4 ? 0 : 128); off < n_feats * 4; off += 256)
+                            asm volatile("prefetch.global.L2 [%0];" ::"l"(row + off));
+                    }
+                }
+            }
             if (!MBAR_WAIT(&tmem_full[full_idx], full_parity)) {
                 if (lane == 0) {
                     atomicOr(status, BFI_STATUS_TIMEOUT);
@@ -504,8 +620,35 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             const int n_chunks = tile_n / 16;
             const int c_beg = (warp - 2) < 4 ? 0 : (n_chunks + 1) / 2;
             const int c_end = (warp - 2) < 4 ? (n_chunks + 1) / 2 : n_chunks;
+            // whole groups of chunks go out through the warp's staging tile, what is left (a ragged
+            // edge of N, rows of C that are not 16-byte aligned, a last odd chunk) straight from the registers
+            int c_direct = c_beg;
+            if (vec_ok) {
+                uint4* stage = reinterpret_cast<uint4*>(smem + TP_RING_BYTES + 256) + (warp - 2) * (TP_STAGE_BYTES / 16);
+                const int m_base = tm * TILE_TOKENS + h * TP_TOKENS + quad * 32;
+                const bool wide = !(epilogue == EPI_SWIGLU || c_dtype == BFI_BF16);      // float32 rows: 2 chunks are 128 bytes
 #pragma unroll 1
-            for (int c = c_beg; c < c_end; ++c) {
+                while (c_direct < c_end) {
+                    const int n0 = tn * tile_n + c_direct * 16;
+                    if (!wide && c_direct + 4 <= c_end && n0 + 64 <= N) {
+                        float v[4][16];
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) tmem_ld16(taddr + (c_direct + g) * 16, v[g]);
+                        tp_emit_group<4>(stage, v, lane, epilogue, c_dtype, C, ldc, m_base, M, n0);
+                        c_direct += 4;
+                    } else if (c_direct + 2 <= c_end && n0 + 32 <= N) {
+                        float v[2][16];
+#pragma unroll
+                        for (int g = 0; g < 2; ++g) tmem_ld16(taddr + (c_direct + g) * 16, v[g]);
+                        tp_emit_group<2>(stage, v, lane, epilogue, c_dtype, C, ldc, m_base, M, n0);
+                        c_direct += 2;
+                    } else {
+                        break;
+                    }
+                }
+            }
+#pragma unroll 1
+            for (int c = c_direct; c < c_end; ++c) {
                 const int n = tn * tile_n + c * 16;
                 if (n >= N) break;
                 float v[16];

@@ -632,14 +632,12 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                     const int n0 = tn * tile_n + c_direct * 16;
                     if (!wide && c_direct + 4 <= c_end && n0 + 64 <= N) {
                         float v[4][16];
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) tmem_ld16(taddr + (c_direct + g) * 16, v[g]);
+                        tmem_ld64(taddr + c_direct * 16, v);
                         tp_emit_group<4>(stage, v, lane, epilogue, c_dtype, C, ldc, m_base, M, n0);
                         c_direct += 4;
                     } else if (c_direct + 2 <= c_end && n0 + 32 <= N) {
                         float v[2][16];
-#pragma unroll
-                        for (int g = 0; g < 2; ++g) tmem_ld16(taddr + (c_direct + g) * 16, v[g]);
+                        tmem_ld32(taddr + c_direct * 16, v);
                         tp_emit_group<2>(stage, v, lane, epilogue, c_dtype, C, ldc, m_base, M, n0);
                         c_direct += 2;
                     } else {

@@ -319,8 +319,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
 // ------------------------------------------------------------------------------------------
 // Many tokens (prompts): tokens on the lanes.  D[128 tokens, tile_n features] per tile, so a thread
-// holds 16 consecutive features of one token after tcgen05.ld and stores them as whole 16-byte
-// words (and SiLU*mul pairs sit in one thread).  The kernel is persistent: each block walks over
+// holds consecutive features of one token after tcgen05.ld (SiLU*mul pairs sit in one thread); they
+// leave through a staging tile in shared memory, as whole rows (tp_emit_group), or, where a group
+// is not whole, straight from the registers as 16-byte words.  The kernel is persistent: each block walks over
 // tiles, and the two halves of tensor memory (2 x 256 columns) alternate as accumulators, so the
 // epilogue of one tile runs while the tensor cores work on the next.  tile_n (a multiple of 16, at
 // most 256) is chosen per product so that the tiles fill whole rounds of the SMs: 2560 features

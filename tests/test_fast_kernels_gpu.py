@@ -471,6 +471,25 @@ def test_gemm_tcgen05_many_tokens_every_tile(tile_n, halves, m, n, k, epi):
     assert tc_status_clear() == 0
 
 
+@pytest.mark.parametrize("m,n,k", [(300, 2560, 512), (129, 1000, 200), (1500, 704, 1024)])
+@pytest.mark.parametrize("epi,out_dtype", [(0, torch.bfloat16), (2, torch.float32), (2, torch.bfloat16), (0, torch.float32)])
+def test_gemm_tcgen05_many_tokens_every_output_type(m, n, k, epi, out_dtype):
+    """The many-row kernel's values leave as whole rows through a staging tile: every kind of
+    output (stored or gated, bfloat16 or float32) with whole groups, a ragged last group and rows
+    past the last token."""
+    g = gen(m + n + epi)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) * 0.05).bfloat16()
+    ref = P.linear(w.float(), a.float())
+    if epi == 2:
+        ref = P.swiglu(ref[:, 0::2], ref[:, 1::2])
+    out = torch.full(tuple(ref.shape), float("nan"), dtype=out_dtype, device=DEV)
+    assert fast().gemm_tcgen05(a.to(DEV), w.to(DEV), out, epi)
+    torch.cuda.synchronize()
+    assert tc_status_clear() == 0
+    assert rel_err(out.float(), ref) < (1e-2 if out_dtype == torch.bfloat16 or epi == 2 else 3e-5)
+
+
 def test_gemm_tcgen05_many_tokens_unaligned_output_rows():
     """An output whose rows are not 16-byte aligned takes the scalar stores and is still right."""
     m, n, k = 300, 200, 512
